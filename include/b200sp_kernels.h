@@ -1,0 +1,115 @@
+/*
+ * b200sp_kernels.h -- inner C-ABI between the aclsparse host layer and the sm_100a kernels.
+ *
+ * The reference keeps its host code and its device code in separate translation units
+ * joined by plain extern "C" launchers that take raw device pointers, a small POD
+ * "tiling" struct and a stream:
+ *   spmv_kernel_do(...)      sparse/spmv/arch22/spmv_host.cpp:29-34
+ *   spmm_kernel_launch(...)  sparse/spmm/arch35/spmm_host.cpp:29-33
+ * The functions below are the B200 counterparts of those two launchers plus the
+ * analysis passes that fill the caller's workspace.  No C++ or torch types cross this
+ * boundary; a foreign-language binding can call it directly with device pointers.
+ *
+ * Every function returns 0 on success or the cudaError_t of the failing runtime call.
+ * Unless stated otherwise nothing here allocates, frees or synchronises: work is
+ * enqueued on `stream` (a cudaStream_t passed as void*, NULL = default stream).
+ */
+#ifndef B200SP_KERNELS_H_
+#define B200SP_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types understood by the kernels (value, vector and output types). */
+typedef enum b200spType_t {
+    B200SP_F32 = 0,
+    B200SP_F16 = 1,
+    B200SP_BF16 = 2,
+    B200SP_I32 = 3,
+    B200SP_I8 = 4
+} b200spType_t;
+
+/* alpha / beta as the kernels take them.  When a *_dev pointer is non-NULL the kernel
+ * reads the scalar from device memory (DEVICE pointer mode); otherwise the host copy of
+ * the matching compute type is used. */
+typedef struct b200spScalars {
+    float alpha_f;
+    float beta_f;
+    int32_t alpha_i;
+    int32_t beta_i;
+    const void *alpha_dev;
+    const void *beta_dev;
+} b200spScalars;
+
+/* ------------------------------------------------------------------ SpMV ------------- */
+
+/* Bytes of workspace the SpMV analysis needs for a rows x * matrix with nnz entries. */
+size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t nnz);
+
+/* Analysis pass: splits the merged (row-end, nnz) sequence of the CSR matrix into
+ * equal tiles and writes the tile table plus zeroed arrival counters into `plan`.
+ * Returns cudaErrorInvalidValue when plan_bytes is too small. */
+int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void *plan, size_t plan_bytes,
+                        void *stream);
+
+/* y = alpha * A * x + beta * y, A in CSR with int32 zero-based indices.
+ * comp_type is B200SP_F32 or B200SP_I32; x has val_type; y has out_type.
+ * `plan` must have been filled by b200sp_spmv_analyze for the same row_ptr / rows / nnz.
+ * With plan == NULL a row-group kernel that needs no workspace is used. */
+int b200sp_spmv_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *x, void *y,
+                       int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars, int comp_type,
+                       int val_type, int out_type, void *plan, void *stream);
+
+/* y = alpha * A^T * x + beta * y (y has `cols` entries).  First scales y by beta, then
+ * scatters alpha * x[i] * a_ij into y[j] with atomic adds.  For 16-bit y an fp32
+ * accumulator of `cols` floats in `scratch` is used (scratch_bytes >= 4 * cols). */
+int b200sp_spmv_trans_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *x,
+                             void *y, int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars,
+                             int comp_type, int val_type, int out_type, void *scratch, size_t scratch_bytes,
+                             void *stream);
+
+/* ------------------------------------------------------------------ SpMM ------------- */
+
+/* Dense operand layout, same meaning as the reference's SpmmTilingData
+ * (sparse/spmm/arch35/spmm.h:49-61): ld in elements, order 0 = row-major, 1 = column-major,
+ * op_b 0 = N, 1 = T. */
+typedef struct b200spSpmmShape {
+    int64_t m;          /* rows of A and C            */
+    int64_t k;          /* cols of A                  */
+    int64_t n;          /* cols of C                  */
+    int64_t nnz;
+    int64_t ldb;
+    int64_t ldc;
+    int32_t order_b;
+    int32_t order_c;
+    int32_t op_b;
+    int32_t kahan;      /* 1 = compensated fp32 accumulation */
+} b200spSpmmShape;
+
+/* Bytes of workspace for the SpMM analysis + long-row partial sums. */
+size_t b200sp_spmm_plan_bytes(int64_t rows, int64_t nnz, int64_t n);
+
+/* Analysis pass: finds rows too long for one warp, cuts them into segments and writes
+ * the segment table into `plan`.  This call synchronises `stream` once to read back
+ * the segment count (4 bytes), returned in *segments. */
+int b200sp_spmm_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, int64_t n, void *plan,
+                        size_t plan_bytes, int32_t *segments, void *stream);
+
+/* C = alpha * A * op(B) + beta * C.  val_type is the type of A and B, out_type of C.
+ * `plan` / `segments` come from b200sp_spmm_analyze on the same row_ptr / rows / nnz / n. */
+int b200sp_spmm_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *B, void *C,
+                       const b200spSpmmShape *shape, const b200spScalars *scalars, int val_type, int out_type,
+                       void *plan, int32_t segments, void *stream);
+
+/* Number of streaming multiprocessors of the current device (cached after the first call). */
+int b200sp_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200SP_KERNELS_H_ */

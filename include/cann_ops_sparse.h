@@ -1,0 +1,243 @@
+/*
+ * cann_ops_sparse.h -- aclsparse C API, CSR SpMV / SpMM path, B200 (sm_100a) build.
+ *
+ * This is the public boundary of libops_sparse.so.  Every type, enumerator order and
+ * function signature below is the one the reference library declares in
+ * include/cann_ops_sparse.h (line ranges are cited per block), so a program written
+ * against the reference for this path recompiles against this header unchanged.
+ * Only the hot path is declared: handle, CSR / dense-vector / dense-matrix
+ * descriptors, and the SpMV / SpMM  GetBufferSize -> Preprocess -> compute triplets.
+ * All pointers named "DEVICE" are CUDA device pointers; descriptors borrow them and
+ * never free them.
+ */
+#ifndef CANN_OPS_SPARSE_H_
+#define CANN_OPS_SPARSE_H_
+
+#include <unistd.h>
+#include <stdint.h>
+#include <acl/acl_base_rt.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums (reference include/cann_ops_sparse.h:24-28, 50-53, 81-95, 98-168, 213-248, 898-901).
+ * Enumerator order is part of the ABI and is kept exactly. ---- */
+
+typedef enum aclsparseOperation_t {
+    ACL_SPARSE_OP_NON_TRANSPOSE = 0,
+    ACL_SPARSE_OP_TRANSPOSE,
+    ACL_SPARSE_OP_CONJUGATE_TRANSPOSE
+} aclsparseOperation_t;
+
+typedef enum aclsparseOrder_t {
+    ACL_SPARSE_ORDER_ROW = 0,
+    ACL_SPARSE_ORDER_COL = 1
+} aclsparseOrder_t;
+
+typedef enum aclsparseSpMMAlg_t {
+    ACL_SPARSE_SPMM_ALG_DEFAULT = 0,
+    ACL_SPARSE_SPMM_CSR_ALG1,
+    /* fp32 only: Kahan-compensated accumulation; ignored for other value types. */
+    ACL_SPARSE_SPMM_CSR_FP32_HIGH_PRECISION_ALG
+} aclsparseSpMMAlg_t;
+
+typedef enum aclsparseStatus_t {
+    ACL_SPARSE_STATUS_SUCCESS = 0,
+    ACL_SPARSE_STATUS_NOT_INITIALIZED,
+    ACL_SPARSE_STATUS_ALLOC_FAILED,
+    ACL_SPARSE_STATUS_INVALID_VALUE,
+    ACL_SPARSE_STATUS_ARCH_MISMATCH,
+    ACL_SPARSE_STATUS_EXECUTION_FAILED,
+    ACL_SPARSE_STATUS_INTERNAL_ERROR,
+    ACL_SPARSE_STATUS_MATRIX_TYPE_NOT_SUPPORTED,
+    ACL_SPARSE_STATUS_NOT_SUPPORTED,
+    ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES,
+    ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR
+} aclsparseStatus_t;
+
+typedef enum aclsparseSpMVAlg_t {
+    ACL_SPARSE_SPMV_ALG_DEFAULT,
+    ACL_SPARSE_SPMV_COO_ALG1,
+    ACL_SPARSE_SPMV_COO_ALG2,
+    ACL_SPARSE_SPMV_CSR_ALG1,
+    ACL_SPARSE_SPMV_CSR_ALG2,
+    ACL_SPARSE_SPMV_SELL_ALG1
+} aclsparseSpMVAlg_t;
+
+typedef enum aclsparseIndexType_t {
+    ACL_SPARSE_INDEX_32I = 0,
+    ACL_SPARSE_INDEX_64I
+} aclsparseIndexType_t;
+
+typedef enum aclsparseIndexBase_t {
+    ACL_SPARSE_INDEX_BASE_ZERO = 0,
+    ACL_SPARSE_INDEX_BASE_ONE
+} aclsparseIndexBase_t;
+
+typedef enum aclsparseFormat_t {
+    ACL_SPARSE_FORMAT_COO = 0,
+    ACL_SPARSE_FORMAT_CSR,
+    ACL_SPARSE_FORMAT_CSC,
+    ACL_SPARSE_FORMAT_BLOCKED_ELL,
+    ACL_SPARSE_FORMAT_SLICED_ELL,
+    ACL_SPARSE_FORMAT_BSR
+} aclsparseFormat_t;
+
+typedef enum aclsparsePointerMode_t {
+    ACL_SPARSE_POINTER_MODE_HOST = 0,
+    ACL_SPARSE_POINTER_MODE_DEVICE = 1
+} aclsparsePointerMode_t;
+
+/* ---- opaque types (reference :30-47) ---- */
+struct aclsparseContext;
+struct aclsparseSpMatDescr;
+struct aclsparseDnVecDescr;
+struct aclsparseDnMatDescr;
+
+typedef struct aclsparseContext *aclsparseHandle_t;
+typedef struct aclsparseSpMatDescr *aclsparseSpMatDescr_t;
+typedef struct aclsparseDnVecDescr *aclsparseDnVecDescr_t;
+typedef struct aclsparseDnMatDescr *aclsparseDnMatDescr_t;
+typedef struct aclsparseSpMatDescr const *aclsparseConstSpMatDescr_t;
+typedef struct aclsparseDnVecDescr const *aclsparseConstDnVecDescr_t;
+typedef struct aclsparseDnMatDescr const *aclsparseConstDnMatDescr_t;
+
+/* ======================================================================================
+ * Handle (reference :817-904; behaviour from sparse/common/aclsparse_auxiliary.cpp:64-198,
+ * 253-279).  Create needs *handle == NULL on entry and allocates a 4 MiB device
+ * workspace; Destroy drains the handle's stream first.  SetWorkspace(NULL) switches back
+ * to the built-in workspace; a user workspace only ever grows.
+ * ====================================================================================== */
+aclsparseStatus_t aclsparseCreate(aclsparseHandle_t *handle);
+aclsparseStatus_t aclsparseDestroy(aclsparseHandle_t handle);
+aclsparseStatus_t aclsparseSetStream(aclsparseHandle_t handle, aclrtStream stream);
+aclsparseStatus_t aclsparseGetStream(aclsparseHandle_t handle, aclrtStream *stream);
+aclsparseStatus_t aclsparseSetWorkspace(aclsparseHandle_t handle, void *workspace, size_t workspaceSize);
+aclsparseStatus_t aclsparseGetWorkspace(aclsparseHandle_t handle, void **workspace, size_t *workspaceSize);
+aclsparseStatus_t aclsparseGetVersion(aclsparseHandle_t handle, int *version);
+aclsparseStatus_t aclsparseSetPointerMode(aclsparseHandle_t handle, aclsparsePointerMode_t mode);
+aclsparseStatus_t aclsparseGetPointerMode(aclsparseHandle_t handle, aclsparsePointerMode_t *mode);
+
+/* ======================================================================================
+ * Dense vector descriptor (reference :259-273, 335-366; sparse/common/aclsparse_descr.cpp:
+ * 96-147, 306-368).  size >= 0; values may be NULL only when size == 0.
+ * DestroyDnVec(NULL) is INVALID_VALUE.
+ * ====================================================================================== */
+aclsparseStatus_t aclsparseCreateDnVec(aclsparseDnVecDescr_t *dnVecDescr, int64_t size, void *values,
+                                       aclDataType valueType);
+aclsparseStatus_t aclsparseCreateConstDnVec(aclsparseConstDnVecDescr_t *dnVecDescr, int64_t size,
+                                            const void *values, aclDataType valueType);
+aclsparseStatus_t aclsparseDestroyDnVec(aclsparseConstDnVecDescr_t dnVecDescr);
+aclsparseStatus_t aclsparseDnVecGet(aclsparseDnVecDescr_t dnVecDescr, int64_t *size, void **values,
+                                    aclDataType *valueType);
+aclsparseStatus_t aclsparseConstDnVecGet(aclsparseConstDnVecDescr_t dnVecDescr, int64_t *size,
+                                         const void **values, aclDataType *valueType);
+aclsparseStatus_t aclsparseDnVecGetValues(aclsparseDnVecDescr_t dnVecDescr, void **values);
+aclsparseStatus_t aclsparseConstDnVecGetValues(aclsparseConstDnVecDescr_t dnVecDescr, const void **values);
+aclsparseStatus_t aclsparseDnVecSetValues(aclsparseDnVecDescr_t dnVecDescr, void *values);
+
+/* ======================================================================================
+ * CSR matrix descriptor (reference :393-402, 443-473; aclsparse_descr.cpp:370-422, 473-492,
+ * 517-586).  Create accepts 32- or 64-bit index types; SpMV / SpMM execute only
+ * (32I, 32I), zero-based.  DestroySpMat(NULL) is SUCCESS.
+ * ====================================================================================== */
+aclsparseStatus_t aclsparseCreateCsr(aclsparseSpMatDescr_t *spMatDescr, int64_t rows, int64_t cols, int64_t nnz,
+                                     void *csrRowOffsets, void *csrColInd, void *csrValues,
+                                     aclsparseIndexType_t csrRowOffsetsType, aclsparseIndexType_t csrColIndType,
+                                     aclsparseIndexBase_t idxBase, aclDataType valueType);
+aclsparseStatus_t aclsparseCreateConstCsr(aclsparseConstSpMatDescr_t *spMatDescr, int64_t rows, int64_t cols,
+                                          int64_t nnz, const void *csrRowOffsets, const void *csrColInd,
+                                          const void *csrValues, aclsparseIndexType_t csrRowOffsetsType,
+                                          aclsparseIndexType_t csrColIndType, aclsparseIndexBase_t idxBase,
+                                          aclDataType valueType);
+aclsparseStatus_t aclsparseCsrSetPointers(aclsparseSpMatDescr_t descr, void *rowOffsets, void *colIndices,
+                                          void *values);
+aclsparseStatus_t aclsparseDestroySpMat(aclsparseConstSpMatDescr_t spMatDescr);
+aclsparseStatus_t aclsparseSpMatGetFormat(aclsparseConstSpMatDescr_t spMatDescr, aclsparseFormat_t *format);
+aclsparseStatus_t aclsparseSpMatGetValues(aclsparseSpMatDescr_t spMatDescr, void **values);
+aclsparseStatus_t aclsparseConstSpMatGetValues(aclsparseConstSpMatDescr_t spMatDescr, const void **values);
+aclsparseStatus_t aclsparseSpMatSetValues(aclsparseSpMatDescr_t spMatDescr, void *values);
+aclsparseStatus_t aclsparseSpMatGetSize(aclsparseConstSpMatDescr_t spMatDescr, int64_t *rows, int64_t *cols,
+                                        int64_t *nnz);
+
+/* ======================================================================================
+ * Dense matrix descriptor (reference :551-614; aclsparse_descr.cpp:588-743).
+ * rows, cols, ld > 0 and values != NULL are required; ld >= cols (row-major) or
+ * ld >= rows (column-major).  DestroyDnMat(NULL) is INVALID_VALUE.
+ * ====================================================================================== */
+aclsparseStatus_t aclsparseCreateDnMat(aclsparseDnMatDescr_t *dnMatDescr, int64_t rows, int64_t cols, int64_t ld,
+                                       void *values, aclDataType valueType, aclsparseOrder_t order);
+aclsparseStatus_t aclsparseCreateConstDnMat(aclsparseConstDnMatDescr_t *dnMatDescr, int64_t rows, int64_t cols,
+                                            int64_t ld, const void *values, aclDataType valueType,
+                                            aclsparseOrder_t order);
+aclsparseStatus_t aclsparseDestroyDnMat(aclsparseConstDnMatDescr_t dnMatDescr);
+aclsparseStatus_t aclsparseDnMatGet(aclsparseDnMatDescr_t dnMatDescr, int64_t *rows, int64_t *cols, int64_t *ld,
+                                    void **values, aclDataType *valueType, aclsparseOrder_t *order);
+aclsparseStatus_t aclsparseConstDnMatGet(aclsparseConstDnMatDescr_t dnMatDescr, int64_t *rows, int64_t *cols,
+                                         int64_t *ld, const void **values, aclDataType *valueType,
+                                         aclsparseOrder_t *order);
+aclsparseStatus_t aclsparseDnMatGetValues(aclsparseDnMatDescr_t dnMatDescr, void **values);
+aclsparseStatus_t aclsparseConstDnMatGetValues(aclsparseConstDnMatDescr_t dnMatDescr, const void **values);
+aclsparseStatus_t aclsparseDnMatSetValues(aclsparseDnMatDescr_t dnMatDescr, void *values);
+
+/* ======================================================================================
+ * SpMV:  y = alpha * op(A) * x + beta * y        (reference :490-533;
+ * host logic sparse/spmv/arch22/spmv_host.cpp:121-295).
+ *
+ * Type rules: x has A's value type; (A/x, y, compute) is one of
+ *   (f32,f32,f32) (f16,f16|f32,f32) (bf16,bf16|f32,f32) (i32,i32,i32) (i32,f32,f32).
+ * alpha / beta point to a float or int32 (by computeType); NULL means alpha = 1, beta = 0.
+ * They are read on the host in HOST pointer mode and by the kernel in DEVICE pointer mode.
+ * x.size >= cols and y.size >= rows (swapped for op = TRANSPOSE).
+ *
+ * The reference declares GetBufferSize / Preprocess but ships no definition; here
+ * they exist.  Preprocess fills `externalBuffer` (>= GetBufferSize bytes) with the
+ * row-length analysis for A's sparsity pattern and records it as A's active buffer; a
+ * later SpMV given the same buffer reuses it.  SpMV with externalBuffer == NULL runs the
+ * analysis in the handle workspace on every call.  All three enqueue on the handle's
+ * stream and return without synchronising.
+ * ====================================================================================== */
+aclsparseStatus_t aclsparseSpMVGetBufferSize(aclsparseHandle_t handle, aclsparseOperation_t opA, const void *alpha,
+                                             aclsparseConstSpMatDescr_t matA, aclsparseConstDnVecDescr_t vecX,
+                                             const void *beta, aclsparseDnVecDescr_t vecY, aclDataType computeType,
+                                             aclsparseSpMVAlg_t alg, size_t *bufferSize);
+aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, aclsparseOperation_t opA, const void *alpha,
+                                          aclsparseConstSpMatDescr_t matA, aclsparseConstDnVecDescr_t vecX,
+                                          const void *beta, aclsparseDnVecDescr_t vecY, aclDataType computeType,
+                                          aclsparseSpMVAlg_t alg, void *externalBuffer);
+aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOperation_t opA, const void *alpha,
+                                aclsparseConstSpMatDescr_t matA, aclsparseConstDnVecDescr_t vecX, const void *beta,
+                                aclsparseDnVecDescr_t vecY, aclDataType computeType, aclsparseSpMVAlg_t alg,
+                                void *externalBuffer);
+
+/* ======================================================================================
+ * SpMM:  C = alpha * A * op(B) + beta * C        (reference :682-704;
+ * host logic sparse/spmm/arch35/spmm_host.cpp:152-394).
+ *
+ * opA = NON_TRANSPOSE only; opB in {N, T}; B and C row- or column-major with ld.
+ * (A, B, C, compute) is one of (f32,f32,f32,f32) (f16,f16,f16,f32) (i8,i8,i32,i32), plus
+ * the B200 extension (bf16,bf16,f32|bf16,f32).  NULL alpha / beta read as 0.
+ * `buffer` must hold GetBufferSize bytes; NULL is INSUFFICIENT_RESOURCES.  SpMM on a
+ * buffer that is not A's active buffer re-runs the analysis into it first.
+ * ====================================================================================== */
+aclsparseStatus_t aclsparseSpMMGetBufferSize(aclsparseHandle_t handle, aclsparseOperation_t opA,
+                                             aclsparseOperation_t opB, const void *alpha,
+                                             aclsparseConstSpMatDescr_t matA, aclsparseConstDnMatDescr_t matB,
+                                             const void *beta, aclsparseDnMatDescr_t matC, aclDataType computeType,
+                                             aclsparseSpMMAlg_t alg, size_t *size);
+aclsparseStatus_t aclsparseSpMMPreprocess(aclsparseHandle_t handle, aclsparseOperation_t opA,
+                                          aclsparseOperation_t opB, const void *alpha,
+                                          aclsparseConstSpMatDescr_t matA, aclsparseConstDnMatDescr_t matB,
+                                          const void *beta, aclsparseDnMatDescr_t matC, aclDataType computeType,
+                                          aclsparseSpMMAlg_t alg, void *buffer);
+aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t opA, aclsparseOperation_t opB,
+                                const void *alpha, aclsparseConstSpMatDescr_t matA,
+                                aclsparseConstDnMatDescr_t matB, const void *beta, aclsparseDnMatDescr_t matC,
+                                aclDataType computeType, aclsparseSpMMAlg_t alg, void *buffer);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CANN_OPS_SPARSE_H_ */

@@ -1,0 +1,586 @@
+// CSR SpMM kernels for sm_100a and their extern "C" launchers.
+//
+// The reference computes one (row, 8-column chunk) per SIMT thread and re-reads the row's
+// col_ind / values once per chunk (sparse/spmm/arch35/spmm_kernel.cpp:88-268).  Here a
+// warp owns a row: the row's col_ind / values are read once, 32 at a time, and handed to
+// the lanes by shuffle; the lanes sit side by side on a row of B, 16 bytes each, so every B
+// row is fetched with full 128-bit coalesced loads.  When a B row is narrower than a warp
+// (N * sizeof < 512 bytes) the warp splits into groups that take alternate non-zeros of
+// the same row and are summed at the end.
+//
+// Row-length routing (the analysis pass fills the workspace):
+//     rows <= 1024 non-zeros            -> one warp per row;
+//     longer rows                       -> cut into segments of 4096 non-zeros, one CTA
+//                                          (4 warps) per segment.  A row of several
+//                                          segments is completed by whichever segment CTA
+//                                          finishes last: it adds the stored partial rows in
+//                                          segment order, so no CTA ever waits and the sum
+//                                          order is fixed.
+// Layouts other than "B rows contiguous, C row-major, 16-byte aligned", and the int8 path,
+// go through a generic one-thread-per-output kernel that uses the reference's index
+// formulas verbatim in meaning (spmm_kernel.cpp:156-168, 215-219).
+//
+// Numerics follow the golden SpmmCpuFp32 / SpmmCpuInt8 (test/spmm/arch35/spmm_test.cpp:
+// 125-200): inputs widened to fp32 (int32), products accumulated in fp32 (int32),
+// C = alpha*acc + beta*C with C not read when beta == 0; fp16 output is clamped to
+// +-65504 before rounding; int32 output is computed in int64 and saturated.
+#include <cstdint>
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "b200sp_kernels.h"
+
+namespace {
+
+constexpr int kThreads = 128;           // 4 warps: 4 rows, or one long-row segment
+constexpr int kWarps = kThreads / 32;
+constexpr int kLongRow = 1024;          // rows longer than this are handled by segment CTAs
+constexpr int kSegNnz = 4096;           // non-zeros per segment
+constexpr int kWarpSegNnz = kSegNnz / kWarps;
+constexpr int kMaxTileCols = 256;       // widest column tile one warp pass covers (32 lanes x 8)
+
+inline size_t AlignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct SegEntry {
+    int32_t row;
+    int32_t seg;      // index of this segment inside its row
+    int32_t longIdx;  // index into the long-row table
+    int32_t pad;
+};
+struct LongRow {
+    int32_t row;
+    int32_t segBase;   // first entry of this row in the segment table
+    int32_t nseg;
+    int32_t partBase;  // first partial-row slot (rows of two or more segments only)
+};
+
+struct PlanLayout {
+    int64_t capLong, capSegs;
+    size_t offCounts, offLong, offSegs, offCounters, offPartials, total;
+};
+
+inline PlanLayout LayoutFor(int64_t rows, int64_t nnz, int64_t n)
+{
+    (void)rows;
+    PlanLayout L;
+    L.capLong = nnz / (kLongRow + 1) + 1;
+    L.capSegs = nnz / kSegNnz + L.capLong + 1;
+    L.offCounts = 0;
+    L.offLong = 256;
+    L.offSegs = AlignUp(L.offLong + sizeof(LongRow) * (size_t)L.capLong, 256);
+    L.offCounters = AlignUp(L.offSegs + sizeof(SegEntry) * (size_t)L.capSegs, 256);
+    L.offPartials = AlignUp(L.offCounters + sizeof(int32_t) * (size_t)L.capLong, 256);
+    // Only rows of two or more segments store partial rows; those have > kSegNnz entries.
+    const int64_t capPartialSegs = 2 * (nnz / kSegNnz) + 1;
+    L.total = AlignUp(L.offPartials + sizeof(float) * (size_t)capPartialSegs * (size_t)n, 256);
+    return L;
+}
+
+// ---------------------------------------------------------------- element helpers
+
+template <typename T> __device__ __forceinline__ float ToF32(T v);
+template <> __device__ __forceinline__ float ToF32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float ToF32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float ToF32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T FromF32(float v);
+template <> __device__ __forceinline__ float FromF32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half FromF32<__half>(float v)
+{
+    // Saturate instead of producing inf (reference spmm_kernel.cpp:232-236).
+    v = fminf(fmaxf(v, -65504.0f), 65504.0f);
+    return __float2half_rn(v);
+}
+template <> __device__ __forceinline__ __nv_bfloat16 FromF32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+struct ScalarsF {
+    float alpha, beta;
+    const float *alphaDev, *betaDev;
+    __device__ __forceinline__ float Alpha() const { return alphaDev ? *alphaDev : alpha; }
+    __device__ __forceinline__ float Beta() const { return betaDev ? *betaDev : beta; }
+};
+struct ScalarsI {
+    int32_t alpha, beta;
+    const int32_t *alphaDev, *betaDev;
+    __device__ __forceinline__ int32_t Alpha() const { return alphaDev ? *alphaDev : alpha; }
+    __device__ __forceinline__ int32_t Beta() const { return betaDev ? *betaDev : beta; }
+};
+
+// 16 bytes of a B row as fp32 values: 4 floats, or 8 half / bf16.
+template <typename T> struct Pack;
+template <> struct Pack<float> {
+    static constexpr int kElems = 4;
+    static __device__ __forceinline__ void Load(const float *p, float (&out)[4])
+    {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(p));
+        out[0] = q.x; out[1] = q.y; out[2] = q.z; out[3] = q.w;
+    }
+};
+template <> struct Pack<__half> {
+    static constexpr int kElems = 8;
+    static __device__ __forceinline__ void Load(const __half *p, float (&out)[8])
+    {
+        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p));
+        const __half2 *h = reinterpret_cast<const __half2 *>(&q);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            out[2 * i] = f.x;
+            out[2 * i + 1] = f.y;
+        }
+    }
+};
+template <> struct Pack<__nv_bfloat16> {
+    static constexpr int kElems = 8;
+    static __device__ __forceinline__ void Load(const __nv_bfloat16 *p, float (&out)[8])
+    {
+        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // bf16 -> fp32 is a 16-bit shift
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+// ---------------------------------------------------------------- analysis
+
+__global__ void SpmmFindLongRowsKernel(const int32_t *__restrict__ rowPtr, int rows, int32_t *counts,
+                                       LongRow *longRows, SegEntry *segs, int32_t *counters)
+{
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        const int len = rowPtr[r + 1] - rowPtr[r];
+        if (len <= kLongRow) continue;
+        const int nseg = (len + kSegNnz - 1) / kSegNnz;
+        const int li = atomicAdd(&counts[0], 1);
+        const int sb = atomicAdd(&counts[1], nseg);
+        const int pb = nseg > 1 ? atomicAdd(&counts[2], nseg) : 0;
+        longRows[li] = {(int32_t)r, sb, nseg, pb};
+        counters[li] = 0;
+        for (int s = 0; s < nseg; ++s) segs[sb + s] = {(int32_t)r, s, li, 0};
+    }
+}
+
+// ---------------------------------------------------------------- fast path
+
+template <typename ValT, typename OutT>
+struct FastArgs {
+    const int32_t *rowPtr;
+    const int32_t *colInd;
+    const ValT *val;
+    const ValT *B;
+    OutT *C;
+    int m;
+    int n;
+    long long ldb;
+    long long ldc;
+    ScalarsF sc;
+    int nsegs;
+    const LongRow *longRows;
+    const SegEntry *segs;
+    int32_t *counters;
+    float *partials;      // [segment][n]
+    int lanesPerRow;      // lanes side by side on one B row, power of two
+};
+
+// Accumulates sum_p val[p] * B[col[p], col0 + lane-slice] over p in [s, e) into acc.
+// All 32 lanes must call it with the same s, e.
+template <typename ValT, bool kKahan, int kUnroll>
+__device__ __forceinline__ void RowDot(const int32_t *__restrict__ colInd, const ValT *__restrict__ val,
+                                       const ValT *__restrict__ Bcol, long long ldb, int s, int e, int lanesPerRow,
+                                       bool colLive, float (&acc)[Pack<ValT>::kElems],
+                                       float (&comp)[Pack<ValT>::kElems])
+{
+    constexpr int E = Pack<ValT>::kElems;
+    const int lane = threadIdx.x & 31;
+    const int groups = 32 / lanesPerRow;
+    const int g = lane / lanesPerRow;
+    for (int p0 = s; p0 < e; p0 += 32) {
+        const int cnt = e - p0 < 32 ? e - p0 : 32;
+        int myCol = 0;
+        float myVal = 0.0f;
+        if (lane < cnt) {
+            myCol = __ldcs(colInd + p0 + lane);
+            myVal = ToF32(__ldcs(val + p0 + lane));
+        }
+        for (int q0 = 0; q0 < cnt; q0 += groups * kUnroll) {
+            float b[kUnroll][E];
+            float v[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int q = q0 + u * groups + g;
+                const int c = __shfl_sync(0xffffffffu, myCol, q & 31);
+                const float vv = __shfl_sync(0xffffffffu, myVal, q & 31);
+                const bool live = colLive && q < cnt;
+                v[u] = live ? vv : 0.0f;
+                if (live) {
+                    Pack<ValT>::Load(Bcol + (long long)c * ldb, b[u]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < E; ++i) b[u][i] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+                for (int i = 0; i < E; ++i) {
+                    if (kKahan) {  // compensated summation, as the reference's high-precision algorithm
+                        const float y = v[u] * b[u][i] - comp[i];
+                        const float t = acc[i] + y;
+                        comp[i] = (t - acc[i]) - y;
+                        acc[i] = t;
+                    } else {
+                        acc[i] = fmaf(v[u], b[u][i], acc[i]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <typename OutT, int E>
+__device__ __forceinline__ void StoreRowSlice(OutT *dst, const float (&acc)[E], float alpha, float beta)
+{
+    float z[E];
+    if (beta != 0.0f) {
+#pragma unroll
+        for (int i = 0; i < E; ++i) z[i] = alpha * acc[i] + beta * ToF32(dst[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) z[i] = alpha * acc[i];
+    }
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+        for (int i = 0; i < E; i += 4)
+            *reinterpret_cast<float4 *>(dst + i) = make_float4(z[i], z[i + 1], z[i + 2], z[i + 3]);
+    } else {
+        static_assert(E == 8, "16-bit output slices are 8 wide");
+        OutT o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = FromF32<OutT>(z[i]);
+        *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(o);
+    }
+}
+
+template <typename ValT, typename OutT, bool kKahan>
+__global__ void __launch_bounds__(kThreads) SpmmFastKernel(const FastArgs<ValT, OutT> a)
+{
+    constexpr int E = Pack<ValT>::kElems;
+    __shared__ float sAcc[kWarps][kMaxTileCols];
+    __shared__ int sLast;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int L = a.lanesPerRow;
+    const int li = lane & (L - 1);
+    const int tileCols = L * E;
+    const float alpha = a.sc.Alpha();
+    const float beta = a.sc.Beta();
+
+    if ((int)blockIdx.x >= a.nsegs) {
+        // ---- one warp per row ----
+        const long long row = (long long)(blockIdx.x - a.nsegs) * kWarps + warp;
+        if (row >= a.m) return;
+        const int s = a.rowPtr[row];
+        const int e = a.rowPtr[row + 1];
+        if (e - s > kLongRow) return;  // owned by segment CTAs
+        for (int col0 = 0; col0 < a.n; col0 += tileCols) {
+            const int col = col0 + li * E;
+            const bool colLive = col < a.n;
+            float acc[E], comp[E];
+#pragma unroll
+            for (int i = 0; i < E; ++i) acc[i] = comp[i] = 0.0f;
+            if (L == 32) RowDot<ValT, kKahan, 8>(a.colInd, a.val, a.B + col, a.ldb, s, e, L, colLive, acc, comp);
+            else RowDot<ValT, kKahan, 4>(a.colInd, a.val, a.B + col, a.ldb, s, e, L, colLive, acc, comp);
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                if (kKahan) acc[i] -= comp[i];
+                for (int off = L; off < 32; off <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+            }
+            if (lane < L && colLive) StoreRowSlice<OutT, E>(a.C + row * a.ldc + col, acc, alpha, beta);
+        }
+        return;
+    }
+
+    // ---- one CTA per long-row segment ----
+    const SegEntry seg = a.segs[blockIdx.x];
+    const LongRow lr = a.longRows[seg.longIdx];
+    const int rowStart = a.rowPtr[seg.row];
+    const int rowEnd = a.rowPtr[seg.row + 1];
+    const int segStart = rowStart + seg.seg * kSegNnz;
+    const int segEnd = segStart + kSegNnz < rowEnd ? segStart + kSegNnz : rowEnd;
+    int ws = segStart + warp * kWarpSegNnz;
+    int we = ws + kWarpSegNnz;
+    if (ws > segEnd) ws = segEnd;
+    if (we > segEnd) we = segEnd;
+    float *partial = a.partials + (long long)(lr.partBase + seg.seg) * a.n;
+
+    for (int col0 = 0; col0 < a.n; col0 += tileCols) {
+        const int col = col0 + li * E;
+        const bool colLive = col < a.n;
+        float acc[E], comp[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) acc[i] = comp[i] = 0.0f;
+        if (L == 32) RowDot<ValT, kKahan, 8>(a.colInd, a.val, a.B + col, a.ldb, ws, we, L, colLive, acc, comp);
+        else RowDot<ValT, kKahan, 4>(a.colInd, a.val, a.B + col, a.ldb, ws, we, L, colLive, acc, comp);
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            if (kKahan) acc[i] -= comp[i];
+            for (int off = L; off < 32; off <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+        }
+        if (lane < L) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) sAcc[warp][li * E + i] = acc[i];
+        }
+        __syncthreads();
+        // warp 0 adds the four warps' slices in warp order
+        if (warp == 0 && lane < L && colLive) {
+            float tot[E];
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                tot[i] = sAcc[0][li * E + i];
+#pragma unroll
+                for (int w = 1; w < kWarps; ++w) tot[i] += sAcc[w][li * E + i];
+            }
+            if (lr.nseg == 1) {
+                StoreRowSlice<OutT, E>(a.C + (long long)seg.row * a.ldc + col, tot, alpha, beta);
+            } else {
+#pragma unroll
+                for (int i = 0; i < E; ++i) partial[col + i] = tot[i];
+            }
+        }
+        __syncthreads();
+    }
+    if (lr.nseg == 1) return;
+
+    // Arrival: the segment that comes last sums all partial rows in segment order.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(a.counters + seg.longIdx, 1);
+        sLast = (old == lr.nseg - 1);
+        if (sLast) a.counters[seg.longIdx] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!sLast) return;
+    __threadfence();
+    const float *first = a.partials + (long long)lr.partBase * a.n;
+    for (int col = threadIdx.x * E; col < a.n; col += kThreads * E) {
+        float tot[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) tot[i] = 0.0f;
+        for (int sgi = 0; sgi < lr.nseg; ++sgi) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) tot[i] += __ldcg(first + (long long)sgi * a.n + col + i);
+        }
+        StoreRowSlice<OutT, E>(a.C + (long long)seg.row * a.ldc + col, tot, alpha, beta);
+    }
+}
+
+// ---------------------------------------------------------------- generic path
+
+struct GenericShape {
+    long long m, n, ldb, ldc;
+    int bRowMajor, cRowMajor, opB, kahan;
+};
+
+__device__ __forceinline__ long long BIndex(const GenericShape &g, long long c, long long j)
+{
+    // op(B)(c, j): same four cases as the golden SpmmCpuFp32 (spmm_test.cpp:142-151).
+    if (!g.opB) return g.bRowMajor ? c * g.ldb + j : j * g.ldb + c;
+    return g.bRowMajor ? j * g.ldb + c : c * g.ldb + j;
+}
+
+template <typename ValT, typename OutT>
+__global__ void __launch_bounds__(256) SpmmGenericFloatKernel(const int32_t *__restrict__ rowPtr,
+                                                               const int32_t *__restrict__ colInd,
+                                                               const ValT *__restrict__ val,
+                                                               const ValT *__restrict__ B, OutT *__restrict__ C,
+                                                               GenericShape g, ScalarsF sc)
+{
+    const float alpha = sc.Alpha();
+    const float beta = sc.Beta();
+    const long long total = g.m * g.n;
+    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total;
+         w += (long long)gridDim.x * blockDim.x) {
+        const long long r = w / g.n;
+        const long long j = w - r * g.n;
+        float acc = 0.0f, comp = 0.0f;
+        const int e = rowPtr[r + 1];
+        for (int p = rowPtr[r]; p < e; ++p) {
+            const float prod = ToF32(val[p]) * ToF32(B[BIndex(g, colInd[p], j)]);
+            if (g.kahan) {
+                const float y = prod - comp;
+                const float t = acc + y;
+                comp = (t - acc) - y;
+                acc = t;
+            } else {
+                acc += prod;
+            }
+        }
+        if (g.kahan) acc -= comp;
+        const long long ci = g.cRowMajor ? r * g.ldc + j : j * g.ldc + r;
+        float z = alpha * acc;
+        if (beta != 0.0f) z += beta * ToF32(C[ci]);
+        C[ci] = FromF32<OutT>(z);
+    }
+}
+
+__global__ void __launch_bounds__(256) SpmmGenericInt8Kernel(const int32_t *__restrict__ rowPtr,
+                                                              const int32_t *__restrict__ colInd,
+                                                              const int8_t *__restrict__ val,
+                                                              const int8_t *__restrict__ B, int32_t *__restrict__ C,
+                                                              GenericShape g, ScalarsI sc)
+{
+    const int32_t alpha = sc.Alpha();
+    const int32_t beta = sc.Beta();
+    const long long total = g.m * g.n;
+    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total;
+         w += (long long)gridDim.x * blockDim.x) {
+        const long long r = w / g.n;
+        const long long j = w - r * g.n;
+        int32_t acc = 0;
+        const int e = rowPtr[r + 1];
+        for (int p = rowPtr[r]; p < e; ++p)
+            acc += (int32_t)val[p] * (int32_t)B[BIndex(g, colInd[p], j)];
+        const long long ci = g.cRowMajor ? r * g.ldc + j : j * g.ldc + r;
+        // int64 epilogue with saturation (reference spmm_kernel.cpp:251-266)
+        long long wide = (long long)alpha * (long long)acc;
+        if (beta != 0) wide += (long long)beta * (long long)C[ci];
+        if (wide > 2147483647LL) wide = 2147483647LL;
+        if (wide < -2147483648LL) wide = -2147483648LL;
+        C[ci] = (int32_t)wide;
+    }
+}
+
+// ---------------------------------------------------------------- host dispatch
+
+ScalarsF MakeF(const b200spScalars *s)
+{
+    return {s->alpha_f, s->beta_f, static_cast<const float *>(s->alpha_dev), static_cast<const float *>(s->beta_dev)};
+}
+ScalarsI MakeI(const b200spScalars *s)
+{
+    return {s->alpha_i, s->beta_i, static_cast<const int32_t *>(s->alpha_dev),
+            static_cast<const int32_t *>(s->beta_dev)};
+}
+
+bool Aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+template <typename ValT, typename OutT>
+int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, const void *B, void *C,
+                const b200spSpmmShape *sh, const b200spScalars *s, void *plan, int32_t segments,
+                cudaStream_t stream)
+{
+    constexpr int E = Pack<ValT>::kElems;
+    // B rows contiguous in memory: (N, row-major) or (T, column-major).
+    const bool bRowsContig = (sh->op_b == 0 && sh->order_b == 0) || (sh->op_b == 1 && sh->order_b == 1);
+    const bool fast = plan != nullptr && bRowsContig && sh->order_c == 0 && sh->n % E == 0 && sh->ldb % E == 0 &&
+                      sh->ldc % E == 0 && Aligned16(B) && Aligned16(C);
+    if (fast) {
+        const PlanLayout L = LayoutFor(sh->m, sh->nnz, sh->n);
+        char *p = static_cast<char *>(plan);
+        FastArgs<ValT, OutT> a;
+        a.rowPtr = rowPtr;
+        a.colInd = colInd;
+        a.val = static_cast<const ValT *>(val);
+        a.B = static_cast<const ValT *>(B);
+        a.C = static_cast<OutT *>(C);
+        a.m = (int)sh->m;
+        a.n = (int)sh->n;
+        a.ldb = sh->ldb;
+        a.ldc = sh->ldc;
+        a.sc = MakeF(s);
+        a.nsegs = segments;
+        a.longRows = reinterpret_cast<const LongRow *>(p + L.offLong);
+        a.segs = reinterpret_cast<const SegEntry *>(p + L.offSegs);
+        a.counters = reinterpret_cast<int32_t *>(p + L.offCounters);
+        a.partials = reinterpret_cast<float *>(p + L.offPartials);
+        int lanes = 1;
+        while (lanes < 32 && lanes * E < sh->n) lanes <<= 1;
+        a.lanesPerRow = lanes;
+        const long long blocks = (long long)segments + (sh->m + kWarps - 1) / kWarps;
+        if (blocks == 0) return 0;
+        if (sh->kahan) SpmmFastKernel<ValT, OutT, true><<<(unsigned)blocks, kThreads, 0, stream>>>(a);
+        else SpmmFastKernel<ValT, OutT, false><<<(unsigned)blocks, kThreads, 0, stream>>>(a);
+        return (int)cudaGetLastError();
+    }
+    GenericShape g{sh->m, sh->n, sh->ldb, sh->ldc, sh->order_b == 0, sh->order_c == 0, sh->op_b, sh->kahan};
+    const long long total = sh->m * sh->n;
+    if (total == 0) return 0;
+    const long long want = (total + 255) / 256;
+    const long long cap = (long long)b200sp_sm_count() * 32;
+    SpmmGenericFloatKernel<ValT, OutT><<<(unsigned)(want < cap ? want : cap), 256, 0, stream>>>(
+        rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(B), static_cast<OutT *>(C), g,
+        MakeF(s));
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t b200sp_spmm_plan_bytes(int64_t rows, int64_t nnz, int64_t n) { return LayoutFor(rows, nnz, n).total; }
+
+int b200sp_spmm_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, int64_t n, void *plan,
+                        size_t plan_bytes, int32_t *segments, void *stream)
+{
+    const PlanLayout L = LayoutFor(rows, nnz, n);
+    if (plan == nullptr || segments == nullptr || plan_bytes < L.total) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *p = static_cast<char *>(plan);
+    cudaError_t e = cudaMemsetAsync(p + L.offCounts, 0, 256, st);
+    if (e != cudaSuccess) return (int)e;
+    if (rows > 0) {
+        const long long want = (rows + 255) / 256;
+        const long long cap = (long long)b200sp_sm_count() * 16;
+        SpmmFindLongRowsKernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
+            row_ptr, (int)rows, reinterpret_cast<int32_t *>(p + L.offCounts),
+            reinterpret_cast<LongRow *>(p + L.offLong), reinterpret_cast<SegEntry *>(p + L.offSegs),
+            reinterpret_cast<int32_t *>(p + L.offCounters));
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    int32_t counts[2] = {0, 0};
+    e = cudaMemcpyAsync(counts, p + L.offCounts, sizeof(counts), cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    *segments = counts[1];
+    return 0;
+}
+
+int b200sp_spmm_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *B, void *C,
+                       const b200spSpmmShape *shape, const b200spScalars *scalars, int val_type, int out_type,
+                       void *plan, int32_t segments, void *stream)
+{
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (val_type == B200SP_F32 && out_type == B200SP_F32)
+        return LaunchFloat<float, float>(row_ptr, col_ind, val, B, C, shape, scalars, plan, segments, st);
+    if (val_type == B200SP_F16 && out_type == B200SP_F16)
+        return LaunchFloat<__half, __half>(row_ptr, col_ind, val, B, C, shape, scalars, plan, segments, st);
+    if (val_type == B200SP_BF16 && out_type == B200SP_BF16)
+        return LaunchFloat<__nv_bfloat16, __nv_bfloat16>(row_ptr, col_ind, val, B, C, shape, scalars, plan,
+                                                         segments, st);
+    if (val_type == B200SP_BF16 && out_type == B200SP_F32)
+        return LaunchFloat<__nv_bfloat16, float>(row_ptr, col_ind, val, B, C, shape, scalars, plan, segments, st);
+    if (val_type == B200SP_I8 && out_type == B200SP_I32) {
+        GenericShape g{shape->m, shape->n, shape->ldb, shape->ldc, shape->order_b == 0, shape->order_c == 0,
+                       shape->op_b, 0};
+        const long long total = shape->m * shape->n;
+        if (total == 0) return 0;
+        const long long want = (total + 255) / 256;
+        const long long cap = (long long)b200sp_sm_count() * 32;
+        SpmmGenericInt8Kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
+            row_ptr, col_ind, static_cast<const int8_t *>(val), static_cast<const int8_t *>(B),
+            static_cast<int32_t *>(C), g, MakeI(scalars));
+        return (int)cudaGetLastError();
+    }
+    return (int)cudaErrorInvalidValue;
+}
+
+}  // extern "C"
