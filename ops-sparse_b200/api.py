@@ -127,10 +127,12 @@ class DnMat:
 
 
 class CsrMatrix:
-    def __init__(self, row_ptr: torch.Tensor, col_ind: torch.Tensor, values: torch.Tensor, rows: int, cols: int):
+    def __init__(self, row_ptr: torch.Tensor, col_ind: torch.Tensor, values: torch.Tensor, rows: int, cols: int,
+                 nnz: int | None = None):
         assert row_ptr.dtype == torch.int32 and col_ind.dtype == torch.int32
         self.row_ptr, self.col_ind, self.values = row_ptr, col_ind, values
-        self.rows, self.cols, self.nnz = rows, cols, col_ind.numel()
+        self.rows, self.cols = rows, cols
+        self.nnz = col_ind.numel() if nnz is None else nnz
         self._d = c_void_p()
         check(lib().aclsparseCreateCsr(byref(self._d), rows, cols, self.nnz, _ptr(row_ptr), _ptr(col_ind),
                                        _ptr(values), ACL_SPARSE_INDEX_32I, ACL_SPARSE_INDEX_32I,

@@ -315,3 +315,47 @@ def ref_spmm_csr_cpu(M, K, N, row_ptr, col_ind, val, B, C, alpha, beta):
     ref_lib("spmm22").ref_spmm_csr_cpu(c_uint64(M), c_uint64(K), c_uint64(N), _p(row_ptr), _p(col_ind), _p(val), _p(B),
                                        _p(C), _p(Y), c_float(alpha), c_float(beta))
     return Y
+
+
+# ---- CPU-baseline timing ----------------------------------------------------------------------
+
+def time_spmv_f32(row_ptr, col_ind, val, x, y, alpha, beta, threads: int, reps: int):
+    """Times `reps` SpMV passes on the host.  Returns (per-pass seconds array, kind): kind is
+    "reference" when the reference harness's own SpmvCpu was timed (oracle/_ref present), else
+    "port" (oracle.cpp).  Argument set-up is outside the clock."""
+    import time
+    row_ptr, col_ind = _c(row_ptr, np.int32), _c(col_ind, np.int32)
+    val, x, y = _c(val, np.float32), _c(x, np.float32), _c(y, np.float32)
+    rows = row_ptr.size - 1
+    per = np.zeros(max(reps, 1), dtype=np.float64)
+    if ref_available("spmv"):
+        fn = ref_lib("spmv").ref_spmv_bench_f32
+        fn.restype = c_double
+        fn(_p(row_ptr), _p(col_ind), _p(val), _p(x), _p(y), c_int64(rows), c_int64(x.size), c_int64(col_ind.size),
+           c_float(alpha), c_float(beta), int(threads), int(reps), _p(per))
+        return per[:reps], "reference"
+    for r in range(reps):
+        t0 = time.perf_counter()
+        spmv_typed(row_ptr, col_ind, val, x, y, alpha, beta, threads=threads)
+        per[r] = time.perf_counter() - t0
+    return per[:reps], "port"
+
+
+def time_spmm_f32(row_ptr, col_ind, val, B, C, alpha, beta, threads: int, reps: int):
+    """Times `reps` SpMM passes (compact row-major fp32) on the host; see time_spmv_f32."""
+    import time
+    row_ptr, col_ind, val = _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(val, np.float32)
+    B, C = _c(B, np.float32), _c(C, np.float32)
+    m, n = C.shape
+    per = np.zeros(max(reps, 1), dtype=np.float64)
+    if ref_available("spmm35"):
+        fn = ref_lib("spmm35").ref_spmm_bench_f32
+        fn.restype = c_double
+        fn(c_int32(m), c_int32(B.shape[0]), c_int32(n), c_int64(col_ind.size), _p(row_ptr), _p(col_ind), _p(val),
+           _p(B), _p(C), c_float(alpha), c_float(beta), int(threads), int(reps), _p(per))
+        return per[:reps], "reference"
+    for r in range(reps):
+        t0 = time.perf_counter()
+        spmm_f32(row_ptr, col_ind, val, B, C, alpha, beta, threads=threads)
+        per[r] = time.perf_counter() - t0
+    return per[:reps], "port"

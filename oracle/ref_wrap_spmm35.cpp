@@ -53,3 +53,42 @@ extern "C" int32_t ref_generate_random_csr(uint32_t seed, int32_t m, int32_t k, 
     std::copy(v.begin(), v.end(), val);
     return rp.back();
 }
+
+// Times the harness's SpmmCpuFp32 itself on compact row-major operands: `reps` passes over rows
+// [0, m), the row loop cut into `threads` static chunks (one SpmmCpuFp32 call per chunk on its
+// slice of the row offsets and of C).  Returns the mean seconds per pass and,
+// when per_pass_seconds is not NULL, the time of each pass.
+#include <thread>
+#include <time.h>
+extern "C" double ref_spmm_bench_f32(int32_t m, int32_t k, int32_t n, int64_t nnz, const int32_t *row_ptr,
+                                     const int32_t *col_ind, const float *val, const float *B, const float *C,
+                                     float alpha, float beta, int threads, int reps, double *per_pass_seconds)
+{
+    if (threads < 1) threads = 1;
+    const std::vector<int32_t> ci(col_ind, col_ind + nnz);
+    const std::vector<float> v(val, val + nnz), b(B, B + (int64_t)k * n);
+    std::vector<std::vector<int32_t>> rp(threads);
+    std::vector<std::vector<float>> cs(threads);
+    const int64_t chunk = ((int64_t)m + threads - 1) / threads;
+    for (int t = 0; t < threads; ++t) {
+        const int64_t lo = std::min<int64_t>(m, t * chunk), hi = std::min<int64_t>(m, lo + chunk);
+        rp[t].assign(row_ptr + lo, row_ptr + hi + 1);
+        cs[t].assign(C + lo * n, C + hi * n);
+    }
+    struct timespec t0, t1, ta, tb;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (int r = 0; r < reps; ++r) {
+        clock_gettime(CLOCK_MONOTONIC, &ta);
+        std::vector<std::thread> pool;
+        for (int t = 0; t < threads; ++t)
+            pool.emplace_back([&, t] {
+                if (rp[t].size() < 2) return;
+                SpmmCpuFp32((int32_t)rp[t].size() - 1, n, rp[t], ci, v, b, n, true, false, &cs[t], n, true, alpha, beta);
+            });
+        for (auto &th : pool) th.join();
+        clock_gettime(CLOCK_MONOTONIC, &tb);
+        if (per_pass_seconds) per_pass_seconds[r] = (tb.tv_sec - ta.tv_sec) + (tb.tv_nsec - ta.tv_nsec) * 1e-9;
+    }
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    return ((t1.tv_sec - t0.tv_sec) + (t1.tv_nsec - t0.tv_nsec) * 1e-9) / (reps > 0 ? reps : 1);
+}

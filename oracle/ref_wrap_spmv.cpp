@@ -59,3 +59,44 @@ extern "C" int ref_spmv_verify_f32(const float *gold, const float *got, int64_t 
     std::vector<float> g(gold, gold + n), r(got, got + n);
     return Verification<float>(g, r, *mare, *mere, GetMixedToleranceParams<float>());
 }
+
+// Times the harness's SpmvCpu<float> itself: `reps` passes over the whole matrix, the row loop cut
+// into `threads` static chunks (one std::thread each, every chunk a separate SpmvCpu call on
+// its slice of the row offsets; per-row arithmetic untouched).  Returns the mean seconds per pass and,
+// when per_pass_seconds is not NULL, the time of each pass.
+#include <thread>
+#include <time.h>
+extern "C" double ref_spmv_bench_f32(const int32_t *row_ptr, const int32_t *col_ind, const float *val,
+                                     const float *x, const float *y, int64_t rows, int64_t cols, int64_t nnz,
+                                     float alpha, float beta, int threads, int reps, double *per_pass_seconds)
+{
+    if (threads < 1) threads = 1;
+    const std::vector<int32_t> ci(col_ind, col_ind + nnz);
+    const std::vector<float> v(val, val + nnz), xv(x, x + cols);
+    std::vector<std::vector<int32_t>> rp(threads);
+    std::vector<std::vector<float>> ys(threads);
+    const int64_t chunk = (rows + threads - 1) / threads;
+    for (int t = 0; t < threads; ++t) {
+        const int64_t lo = std::min<int64_t>(rows, t * chunk), hi = std::min<int64_t>(rows, lo + chunk);
+        rp[t].assign(row_ptr + lo, row_ptr + hi + 1);  // offsets stay global: they index ci / v directly
+        ys[t].assign(y + lo, y + hi);
+    }
+    volatile float sink = 0.0f;
+    struct timespec t0, t1, ta, tb;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (int r = 0; r < reps; ++r) {
+        clock_gettime(CLOCK_MONOTONIC, &ta);
+        std::vector<std::thread> pool;
+        for (int t = 0; t < threads; ++t)
+            pool.emplace_back([&, t] {
+                if (rp[t].size() < 2) return;
+                std::vector<float> z = SpmvCpu<float, float, float>(rp[t], ci, v, xv, ys[t], alpha, beta);
+                sink = sink + z[0];
+            });
+        for (auto &th : pool) th.join();
+        clock_gettime(CLOCK_MONOTONIC, &tb);
+        if (per_pass_seconds) per_pass_seconds[r] = (tb.tv_sec - ta.tv_sec) + (tb.tv_nsec - ta.tv_nsec) * 1e-9;
+    }
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    return ((t1.tv_sec - t0.tv_sec) + (t1.tv_nsec - t0.tv_nsec) * 1e-9) / (reps > 0 ? reps : 1);
+}

@@ -45,3 +45,14 @@ def assert_rowwise(got64: np.ndarray, gold64: np.ndarray, scale: np.ndarray, tol
         raise AssertionError(f"{what}: {int(bad.sum())} of {err.size} outputs outside tol {tol:g}; "
                              f"worst at flat index {i}: got {got64.ravel()[i]!r} gold {gold64.ravel()[i]!r} "
                              f"scale {scale.ravel()[i]!r}")
+
+
+def make_csr(device, rp, ci, val, vt, rows, cols):
+    """CSR descriptor over storage arrays.  Empty index / value arrays are given one padding
+    element, because the API (like the reference) rejects null CSR pointers."""
+    from ops_sparse_b200 import api
+
+    nnz = int(ci.size)
+    d_ci = torch.from_numpy(np.ascontiguousarray(ci)).to(device) if nnz else torch.zeros(1, dtype=torch.int32, device=device)
+    d_val = to_device(val, vt, device) if nnz else torch.zeros(1, dtype=TORCH_OF[vt], device=device)
+    return api.CsrMatrix(torch.from_numpy(np.ascontiguousarray(rp)).to(device), d_ci, d_val, rows, cols, nnz=nnz)

@@ -1,0 +1,273 @@
+"""GPU: CSR SpMV through the aclsparse C API against the CPU oracle and the golden fixtures."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def run_spmv(h, device, oracle, rp, ci, val, x, y, alpha, beta, vt, ot, trans=False, rows=None, cols=None,
+             mode="plan"):
+    """Uploads storage-typed arrays, runs aclsparseSpMV, returns y in oracle storage."""
+    from ops_sparse_b200 import api, ACL_SPARSE_OP_TRANSPOSE, ACL_SPARSE_OP_NON_TRANSPOSE
+
+    rows = rows if rows is not None else rp.size - 1
+    A = helpers.make_csr(device, rp, ci, val, vt, rows, cols)
+    dx = api.DnVec(helpers.to_device(x, vt, device))
+    dy = api.DnVec(helpers.to_device(y, ot, device))
+    op = ACL_SPARSE_OP_TRANSPOSE if trans else ACL_SPARSE_OP_NON_TRANSPOSE
+    buf = None
+    if mode == "plan":
+        buf = api.spmv_preprocess(h, A, dx, dy, op)
+    elif mode == "buffer-no-preprocess":
+        buf = torch.empty(api.spmv_buffer_size(h, A, dx, dy, op), dtype=torch.uint8, device=device)
+    api.spmv(h, A, dx, dy, alpha, beta, op=op, buffer=buf)
+    if mode == "plan":  # a second call on the same plan must give the same bits (counters self-reset)
+        first = dy.values.clone()
+        dy2 = api.DnVec(helpers.to_device(y, ot, device))
+        api.spmv(h, A, dx, dy2, alpha, beta, op=op, buffer=buf)
+        torch.cuda.synchronize()
+        if not trans:
+            assert torch.equal(first.view(torch.uint8), dy2.values.view(torch.uint8)), "second run differs"
+    torch.cuda.synchronize()
+    return helpers.to_host(dy.values, ot)
+
+
+def check_against_oracle(oracle, rp, ci, val, x, y, alpha, beta, vt, ot, got, trans=False, cols=None, what=""):
+    comp = "i32" if ot == "i32" else "f32"
+    gold = oracle.spmv_typed(rp, ci, val, x, y, alpha, beta, comp, vt, ot, trans=trans, cols=cols)
+    if ot == "i32":
+        assert np.array_equal(got, gold), what
+        return
+    g64 = oracle.from_storage(gold, ot).astype(np.float64)
+    r64 = oracle.from_storage(got, ot).astype(np.float64)
+    y64 = oracle.from_storage(y, ot).astype(np.float64)
+    if trans and ot in ("f16", "bf16"):
+        # The transposed golden rounds its running sums to 16 bits after every update; the kernel
+        # accumulates in fp32 and rounds once, so only the harness's own mixed tolerance applies.
+        ok, st = oracle.verify_mixed(g64, r64, ot)
+        assert ok, (what, st)
+        return
+    if trans:
+        # scale_j = |alpha| * sum_i |a_ij x_i| + |beta y_j|, accumulated column-wise
+        rows = rp.size - 1
+        prod = np.abs(oracle.from_storage(val, vt).astype(np.float64) *
+                      np.repeat(oracle.from_storage(x, vt).astype(np.float64), np.diff(rp)))
+        scale = np.bincount(ci, weights=prod, minlength=cols)[:cols] * abs(alpha) + np.abs(beta * y64)
+    else:
+        scale = abs(alpha) * oracle.spmv_abs_rowsum(rp, ci, val, x, vt) + np.abs(beta * y64)
+    tol = helpers.TOL["f32" if vt in ("f32", "i32") else vt]
+    if ot in ("f16", "bf16"):  # plus half an ulp of the 16-bit output
+        scale = scale + np.abs(g64) * (2.0 ** -11 if ot == "f16" else 2.0 ** -8) / tol
+    helpers.assert_rowwise(r64, g64, scale, tol, what)
+
+
+def random_csr(rng, M, N, lengths):
+    rp = np.zeros(M + 1, np.int32)
+    rp[1:] = np.cumsum(lengths)
+    from ops_sparse_b200 import synth
+    ci = synth.columns_for_lengths(rng, lengths, N)
+    return rp, ci
+
+
+def draw(rng, oracle, n, t, lo=-1.0, hi=1.0):
+    if t == "i32":
+        return rng.integers(-9, 10, n).astype(np.int32)
+    return oracle.to_storage(rng.uniform(lo, hi, n).astype(np.float32), t)
+
+
+@pytest.mark.parametrize("mode", ["plan", "workspace", "buffer-no-preprocess"])
+def test_config1_shape(handle, device, oracle, mode):
+    """4096 x 4096, exactly 16 nnz per row, alpha = 1, beta = 0 (the reference harness's golden path)."""
+    from ops_sparse_b200 import synth
+    c = synth.config1()
+    A = c["A"]
+    got = run_spmv(handle, device, oracle, A.row_ptr, A.col_ind, A.values, c["x"], c["y"], 1.0, 0.0, "f32", "f32",
+                   cols=A.cols, mode=mode)
+    check_against_oracle(oracle, A.row_ptr, A.col_ind, A.values, c["x"], c["y"], 1.0, 0.0, "f32", "f32", got,
+                         what=f"config1/{mode}")
+    ok, st = oracle.verify_mixed(oracle.spmv_typed(A.row_ptr, A.col_ind, A.values, c["x"], c["y"], 1.0, 0.0), got)
+    assert ok, st
+
+
+@pytest.mark.parametrize("rows", [1 << 12, 1 << 16])
+def test_config2_powerlaw_scaled(handle, device, oracle, rows):
+    from ops_sparse_b200 import synth
+    c = synth.config2(rows=rows)
+    A = c["A"]
+    got = run_spmv(handle, device, oracle, A.row_ptr, A.col_ind, A.values, c["x"], c["y"], c["alpha"], c["beta"],
+                   "f32", "f32", cols=A.cols)
+    check_against_oracle(oracle, A.row_ptr, A.col_ind, A.values, c["x"], c["y"], c["alpha"], c["beta"], "f32", "f32",
+                         got, what=f"config2/{rows}")
+
+
+def test_config3_stencil_f16(handle, device, oracle):
+    from ops_sparse_b200 import synth
+    c = synth.config3(grid=40)
+    A = c["A"]
+    val, x = oracle.to_storage(A.values, "f16"), oracle.to_storage(c["x"], "f16")
+    got = run_spmv(handle, device, oracle, A.row_ptr, A.col_ind, val, x, c["y"], 1.0, 0.0, "f16", "f32", cols=A.cols)
+    check_against_oracle(oracle, A.row_ptr, A.col_ind, val, x, c["y"], 1.0, 0.0, "f16", "f32", got, what="config3")
+
+
+TRIPLES = [("f32", "f32"), ("f16", "f32"), ("f16", "f16"), ("bf16", "f32"), ("bf16", "bf16"), ("i32", "i32"),
+           ("i32", "f32")]
+
+
+@pytest.mark.parametrize("vt,ot", TRIPLES)
+@pytest.mark.parametrize("trans", [False, True])
+def test_type_triples(handle, device, oracle, vt, ot, trans):
+    rng = np.random.default_rng(abs(hash((vt, ot, trans))) % 2**32)
+    M, N = 3000, 2500
+    lengths = rng.integers(0, 60, size=M)
+    lengths[::97] = 0
+    lengths[5] = 2400  # one long row
+    rp, ci = random_csr(rng, M, N, lengths)
+    xs, ys = (M, N) if trans else (N, M)
+    val, x, y = draw(rng, oracle, rp[-1], vt), draw(rng, oracle, xs, vt), draw(rng, oracle, ys, ot)
+    a, b = (3, -2) if ot == "i32" else (1.5, -0.5)
+    got = run_spmv(handle, device, oracle, rp, ci, val, x, y, a, b, vt, ot, trans=trans, rows=M, cols=N)
+    check_against_oracle(oracle, rp, ci, val, x, y, a, b, vt, ot, got, trans=trans, cols=N,
+                         what=f"{vt}->{ot} trans={trans}")
+
+
+def test_every_row_length_0_to_130(handle, device, oracle):
+    """Rows of every length 0..130 in random order: exercises each lane-group width and the tile seams."""
+    rng = np.random.default_rng(42)
+    lengths = np.tile(np.arange(0, 131), 40)
+    rng.shuffle(lengths)
+    M, N = lengths.size, 5000
+    rp, ci = random_csr(rng, M, N, lengths)
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    for mode in ("plan", "workspace"):
+        got = run_spmv(handle, device, oracle, rp, ci, val, x, y, -0.75, 2.0, "f32", "f32", cols=N, mode=mode)
+        check_against_oracle(oracle, rp, ci, val, x, y, -0.75, 2.0, "f32", "f32", got, what=f"lengths/{mode}")
+
+
+@pytest.mark.parametrize("shape", ["all_empty", "one_row_huge", "many_empty_then_long", "single_entry", "tall_thin"])
+def test_edge_shapes(handle, device, oracle, shape):
+    rng = np.random.default_rng(7)
+    if shape == "all_empty":
+        M, N, lengths = 10000, 50, np.zeros(10000, np.int64)
+    elif shape == "one_row_huge":
+        M, N, lengths = 1, 200000, np.array([150000])
+    elif shape == "many_empty_then_long":
+        M, N = 20000, 40000
+        lengths = np.zeros(M, np.int64)
+        lengths[-1] = 30000
+        lengths[12345] = 9000
+    elif shape == "single_entry":
+        M, N, lengths = 1, 1, np.array([1])
+    else:
+        M, N, lengths = 100000, 3, rng.integers(0, 4, size=100000)
+    rp, ci = random_csr(rng, M, N, lengths)
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    for beta in (0.0, 0.5):
+        got = run_spmv(handle, device, oracle, rp, ci, val, x, y, 1.25, beta, "f32", "f32", rows=M, cols=N)
+        check_against_oracle(oracle, rp, ci, val, x, y, 1.25, beta, "f32", "f32", got, what=f"{shape}/beta={beta}")
+
+
+def test_beta_zero_ignores_nan_in_y(handle, device, oracle):
+    rng = np.random.default_rng(3)
+    M, N = 2000, 2000
+    rp, ci = random_csr(rng, M, N, rng.integers(0, 20, size=M))
+    val, x = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32")
+    y = np.full(M, np.nan, np.float32)
+    got = run_spmv(handle, device, oracle, rp, ci, val, x, y, 1.0, 0.0, "f32", "f32", cols=N)
+    assert np.isfinite(got).all()
+    check_against_oracle(oracle, rp, ci, val, x, np.zeros(M, np.float32), 1.0, 0.0, "f32", "f32", got, what="nan-y")
+
+
+def test_device_pointer_mode(handle, device, oracle):
+    from ops_sparse_b200 import api
+    rng = np.random.default_rng(9)
+    M, N = 5000, 4000
+    rp, ci = random_csr(rng, M, N, rng.integers(0, 50, size=M))
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    A = api.CsrMatrix(torch.from_numpy(rp).to(device), torch.from_numpy(ci).to(device),
+                      torch.from_numpy(val).to(device), M, N)
+    dx, dy = api.DnVec(torch.from_numpy(x).to(device)), api.DnVec(torch.from_numpy(y).to(device))
+    handle.set_pointer_mode_device(True)
+    a = torch.tensor([2.5], dtype=torch.float32, device=device)
+    b = torch.tensor([-0.5], dtype=torch.float32, device=device)
+    buf = api.spmv_preprocess(handle, A, dx, dy)
+    api.spmv(handle, A, dx, dy, a, b, buffer=buf)
+    torch.cuda.synchronize()
+    handle.set_pointer_mode_device(False)
+    check_against_oracle(oracle, rp, ci, val, x, y, 2.5, -0.5, "f32", "f32", dy.values.cpu().numpy(), what="devptr")
+
+
+def test_unaligned_value_pointers(handle, device, oracle):
+    """col_ind / values views that start 4 bytes into an allocation take the scalar-load kernel."""
+    from ops_sparse_b200 import api
+    rng = np.random.default_rng(10)
+    M, N = 4000, 3000
+    rp, ci = random_csr(rng, M, N, rng.integers(0, 40, size=M))
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    ci_pad = torch.zeros(ci.size + 1, dtype=torch.int32, device=device)
+    ci_pad[1:] = torch.from_numpy(ci).to(device)
+    v_pad = torch.zeros(val.size + 1, dtype=torch.float32, device=device)
+    v_pad[1:] = torch.from_numpy(val).to(device)
+    A = api.CsrMatrix(torch.from_numpy(rp).to(device), ci_pad[1:], v_pad[1:], M, N)
+    assert A.col_ind.data_ptr() % 16 != 0
+    dx, dy = api.DnVec(torch.from_numpy(x).to(device)), api.DnVec(torch.from_numpy(y).to(device))
+    buf = api.spmv_preprocess(handle, A, dx, dy)
+    api.spmv(handle, A, dx, dy, 1.0, 1.0, buffer=buf)
+    torch.cuda.synchronize()
+    check_against_oracle(oracle, rp, ci, val, x, y, 1.0, 1.0, "f32", "f32", dy.values.cpu().numpy(), what="unaligned")
+
+
+def test_golden_fixture_spmv(handle, device, oracle, golden_dir):
+    """The committed fixtures (reference SpmvCpu / SpmvTransCpu outputs): exact for int32, the
+    reference harness's own mixed-tolerance verdict for floating point."""
+    z = np.load(golden_dir / "spmv.npz")
+    for i in range(int(z["count"][0])):
+        comp, vt, ot = (str(s) for s in z[f"{i}/types"])
+        M, N, trans = (int(v) for v in z[f"{i}/dims"])
+        a, b = z[f"{i}/scalars"]
+        a, b = (int(a), int(b)) if comp == "i32" else (float(a), float(b))
+        got = run_spmv(handle, device, oracle, z[f"{i}/row_ptr"], z[f"{i}/col_ind"], z[f"{i}/val"], z[f"{i}/x"],
+                       z[f"{i}/y"], a, b, vt, ot, trans=bool(trans), rows=M, cols=N)
+        gold = z[f"{i}/gold"]
+        if ot == "i32":
+            assert np.array_equal(got, gold), i
+        else:
+            ok, st = oracle.verify_mixed(oracle.from_storage(gold, ot), oracle.from_storage(got, ot), ot)
+            assert ok, (i, comp, vt, ot, trans, st)
+
+
+def test_status_codes_on_device(handle, device, pkg):
+    """Argument errors reported by the compute entry point (spmv_host.cpp:132-274 of the reference)."""
+    from ctypes import byref, c_float, c_size_t, c_void_p, cast
+    from ops_sparse_b200 import api
+    L = pkg.lib()
+    rp = torch.tensor([0, 1, 2], dtype=torch.int32, device=device)
+    ci = torch.tensor([0, 1], dtype=torch.int32, device=device)
+    v = torch.ones(2, dtype=torch.float32, device=device)
+    A = api.CsrMatrix(rp, ci, v, 2, 2)
+    x, y = api.DnVec(torch.ones(2, device=device)), api.DnVec(torch.zeros(2, device=device))
+    one = c_float(1.0)
+    al = cast(byref(one), c_void_p)
+    S = pkg
+    assert L.aclsparseSpMV(None, 0, al, A.raw, x.raw, al, y.raw, S.ACL_FLOAT, 0, None) == S.ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR
+    assert L.aclsparseSpMV(handle.raw, 0, al, None, x.raw, al, y.raw, S.ACL_FLOAT, 0, None) == S.ACL_SPARSE_STATUS_INVALID_VALUE
+    assert L.aclsparseSpMV(handle.raw, 0, al, A.raw, x.raw, al, y.raw, S.ACL_FLOAT, 3, None) == S.ACL_SPARSE_STATUS_NOT_SUPPORTED
+    assert L.aclsparseSpMV(handle.raw, 0, al, A.raw, x.raw, al, y.raw, S.ACL_DOUBLE, 0, None) == S.ACL_SPARSE_STATUS_NOT_SUPPORTED
+    assert L.aclsparseSpMV(handle.raw, 2, al, A.raw, x.raw, al, y.raw, S.ACL_FLOAT, 0, None) == S.ACL_SPARSE_STATUS_NOT_SUPPORTED
+    short = api.DnVec(torch.ones(1, device=device))
+    assert L.aclsparseSpMV(handle.raw, 0, al, A.raw, short.raw, al, y.raw, S.ACL_FLOAT, 0, None) == S.ACL_SPARSE_STATUS_INVALID_VALUE
+    xh = api.DnVec(torch.ones(2, device=device, dtype=torch.float16))
+    assert L.aclsparseSpMV(handle.raw, 0, al, A.raw, xh.raw, al, y.raw, S.ACL_FLOAT, 0, None) == S.ACL_SPARSE_STATUS_NOT_SUPPORTED
+    assert L.aclsparseSpMV(handle.raw, 0, al, A.raw, x.raw, al, y.raw, S.ACL_INT32, 0, None) == S.ACL_SPARSE_STATUS_NOT_SUPPORTED
+    size = c_size_t()
+    assert L.aclsparseSpMVGetBufferSize(handle.raw, 0, al, A.raw, x.raw, al, y.raw, S.ACL_FLOAT, 0, byref(size)) == 0
+    assert size.value > 0
+    assert L.aclsparseSpMVPreprocess(handle.raw, 0, al, A.raw, x.raw, al, y.raw, S.ACL_FLOAT, 0, None) == S.ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES
+    # NULL alpha / beta mean 1 / 0
+    assert L.aclsparseSpMV(handle.raw, 0, None, A.raw, x.raw, None, y.raw, S.ACL_FLOAT, 0, None) == 0
+    torch.cuda.synchronize()
+    assert y.values.tolist() == [1.0, 1.0]
