@@ -1,15 +1,17 @@
 // CSR SpMM kernels for sm_100a and their extern "C" launchers.
 //
 // The reference computes one (row, 8-column chunk) per SIMT thread and re-reads the row's
-// col_ind / values once per chunk (sparse/spmm/arch35/spmm_kernel.cpp:88-268).  Here a
-// warp owns a row: the row's col_ind / values are read once, 32 at a time, and handed to
-// the lanes by shuffle; the lanes sit side by side on a row of B, 16 bytes each, so every B
-// row is fetched with full 128-bit coalesced loads.  When a B row is narrower than a warp
-// (N * sizeof < 512 bytes) the warp splits into groups that take alternate non-zeros of
-// the same row and are summed at the end.
+// col_ind / values once per chunk (sparse/spmm/arch35/spmm_kernel.cpp:88-268).  Here a group
+// of lanes owns a row: the lanes sit side by side on a row of B, 16 bytes each (so every B
+// row is fetched with 128-bit coalesced loads), the row's col_ind / values are read once,
+// one per lane, and handed round the group by shuffle.  A group is as wide as a B row needs
+// (N * sizeof / 16 lanes, a power of two up to 32), so one warp carries 1 to 32 rows of A.
+// Each output keeps one fp32 accumulator that takes its products in CSR order with separate
+// multiply and add, exactly as the golden does: for rows of up to 1024 entries the result is
+// bit-identical to the golden.
 //
 // Row-length routing (the analysis pass fills the workspace):
-//     rows <= 1024 non-zeros            -> one warp per row;
+//     rows <= 1024 non-zeros            -> one lane group per row;
 //     longer rows                       -> cut into segments of 4096 non-zeros, one CTA
 //                                          (4 warps) per segment.  A row of several
 //                                          segments is completed by whichever segment CTA
@@ -183,59 +185,67 @@ struct FastArgs {
     const LongRow *longRows;
     const SegEntry *segs;
     int32_t *counters;
-    float *partials;      // [segment][n]
-    int lanesPerRow;      // lanes side by side on one B row, power of two
+    float *partials;      // [partial slot][n]
 };
 
-// Accumulates sum_p val[p] * B[col[p], col0 + lane-slice] over p in [s, e) into acc.
-// All 32 lanes must call it with the same s, e.
-template <typename ValT, bool kKahan, int kUnroll>
+// One accumulation step, in the golden's arithmetic: the product is rounded, then added
+// (no fused multiply-add), so a row summed in CSR order reproduces the golden bit for bit.
+template <bool kKahan>
+__device__ __forceinline__ void Accumulate(float v, float b, float &acc, float &comp)
+{
+    const float prod = __fmul_rn(v, b);
+    if (kKahan) {  // compensated summation, the reference's high-precision algorithm
+        const float y = __fsub_rn(prod, comp);
+        const float t = __fadd_rn(acc, y);
+        comp = __fsub_rn(__fsub_rn(t, acc), y);
+        acc = t;
+    } else {
+        acc = __fadd_rn(acc, prod);
+    }
+}
+
+// Adds sum_{p in [s, e)} val[p] * B[col[p], slice] to acc, p ascending.  The kLanes lanes of a
+// group call it together with the same s, e (groups of one warp may differ); `trips` is the
+// warp-uniform number of kLanes-wide chunks to walk (>= this group's own need).
+template <typename ValT, bool kKahan, int kLanes>
 __device__ __forceinline__ void RowDot(const int32_t *__restrict__ colInd, const ValT *__restrict__ val,
-                                       const ValT *__restrict__ Bcol, long long ldb, int s, int e, int lanesPerRow,
+                                       const ValT *__restrict__ Bslice, long long ldb, int s, int e, int trips,
                                        bool colLive, float (&acc)[Pack<ValT>::kElems],
                                        float (&comp)[Pack<ValT>::kElems])
 {
     constexpr int E = Pack<ValT>::kElems;
-    const int lane = threadIdx.x & 31;
-    const int groups = 32 / lanesPerRow;
-    const int g = lane / lanesPerRow;
-    for (int p0 = s; p0 < e; p0 += 32) {
-        const int cnt = e - p0 < 32 ? e - p0 : 32;
+    constexpr int kBatch = kLanes < 8 ? kLanes : 8;  // B rows in flight per lane
+    const int li = threadIdx.x & (kLanes - 1);
+    for (int chunk = 0; chunk < trips; ++chunk) {
+        const int p0 = s + chunk * kLanes;
         int myCol = 0;
         float myVal = 0.0f;
-        if (lane < cnt) {
-            myCol = __ldcs(colInd + p0 + lane);
-            myVal = ToF32(__ldcs(val + p0 + lane));
+        if (p0 + li < e) {
+            myCol = __ldcs(colInd + p0 + li);
+            myVal = ToF32(__ldcs(val + p0 + li));
         }
-        for (int q0 = 0; q0 < cnt; q0 += groups * kUnroll) {
-            float b[kUnroll][E];
-            float v[kUnroll];
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                const int q = q0 + u * groups + g;
-                const int c = __shfl_sync(0xffffffffu, myCol, q & 31);
-                const float vv = __shfl_sync(0xffffffffu, myVal, q & 31);
-                const bool live = colLive && q < cnt;
-                v[u] = live ? vv : 0.0f;
-                if (live) {
-                    Pack<ValT>::Load(Bcol + (long long)c * ldb, b[u]);
+        for (int q0 = 0; q0 < kLanes; q0 += kBatch) {
+            float b[kBatch][E];
+            float v[kBatch];
+            bool live[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int c = __shfl_sync(0xffffffffu, myCol, q0 + u, kLanes);
+                v[u] = __shfl_sync(0xffffffffu, myVal, q0 + u, kLanes);
+                live[u] = colLive && (p0 + q0 + u < e);
+                if (live[u]) {
+                    Pack<ValT>::Load(Bslice + (long long)c * ldb, b[u]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < E; ++i) b[u][i] = 0.0f;
                 }
             }
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
+            for (int u = 0; u < kBatch; ++u) {
+                if (live[u]) {
 #pragma unroll
-                for (int i = 0; i < E; ++i) {
-                    if (kKahan) {  // compensated summation, as the reference's high-precision algorithm
-                        const float y = v[u] * b[u][i] - comp[i];
-                        const float t = acc[i] + y;
-                        comp[i] = (t - acc[i]) - y;
-                        acc[i] = t;
-                    } else {
-                        acc[i] = fmaf(v[u], b[u][i], acc[i]);
-                    }
+                    for (int i = 0; i < E; ++i) Accumulate<kKahan>(v[u], b[u][i], acc[i], comp[i]);
                 }
             }
         }
@@ -248,10 +258,10 @@ __device__ __forceinline__ void StoreRowSlice(OutT *dst, const float (&acc)[E], 
     float z[E];
     if (beta != 0.0f) {
 #pragma unroll
-        for (int i = 0; i < E; ++i) z[i] = alpha * acc[i] + beta * ToF32(dst[i]);
+        for (int i = 0; i < E; ++i) z[i] = __fadd_rn(__fmul_rn(alpha, acc[i]), __fmul_rn(beta, ToF32(dst[i])));
     } else {
 #pragma unroll
-        for (int i = 0; i < E; ++i) z[i] = alpha * acc[i];
+        for (int i = 0; i < E; ++i) z[i] = __fmul_rn(alpha, acc[i]);
     }
     if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
@@ -259,86 +269,105 @@ __device__ __forceinline__ void StoreRowSlice(OutT *dst, const float (&acc)[E], 
             *reinterpret_cast<float4 *>(dst + i) = make_float4(z[i], z[i + 1], z[i + 2], z[i + 3]);
     } else {
         static_assert(E == 8, "16-bit output slices are 8 wide");
-        OutT o[8];
+        alignas(16) OutT o[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = FromF32<OutT>(z[i]);
         *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(o);
     }
 }
 
-template <typename ValT, typename OutT, bool kKahan>
+// kLanes lanes lie side by side on one row of B (16 bytes each); a warp therefore carries
+// 32 / kLanes rows of A at once.  Rows of up to kLongRow entries are summed by their group in
+// CSR order; longer rows belong to the segment CTAs at the front of the grid.
+template <typename ValT, typename OutT, bool kKahan, int kLanes>
 __global__ void __launch_bounds__(kThreads) SpmmFastKernel(const FastArgs<ValT, OutT> a)
 {
     constexpr int E = Pack<ValT>::kElems;
+    constexpr int kRowsPerWarp = 32 / kLanes;
+    constexpr int kTileCols = kLanes * E;
     __shared__ float sAcc[kWarps][kMaxTileCols];
     __shared__ int sLast;
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int L = a.lanesPerRow;
-    const int li = lane & (L - 1);
-    const int tileCols = L * E;
+    const int li = lane & (kLanes - 1);
     const float alpha = a.sc.Alpha();
     const float beta = a.sc.Beta();
 
     if ((int)blockIdx.x >= a.nsegs) {
-        // ---- one warp per row ----
-        const long long row = (long long)(blockIdx.x - a.nsegs) * kWarps + warp;
-        if (row >= a.m) return;
-        const int s = a.rowPtr[row];
-        const int e = a.rowPtr[row + 1];
-        if (e - s > kLongRow) return;  // owned by segment CTAs
-        for (int col0 = 0; col0 < a.n; col0 += tileCols) {
+        // ---- one lane group per row ----
+        const long long row = ((long long)(blockIdx.x - a.nsegs) * kWarps + warp) * kRowsPerWarp + lane / kLanes;
+        int s = 0, e = 0;
+        if (row < a.m) {
+            s = a.rowPtr[row];
+            e = a.rowPtr[row + 1];
+            if (e - s > kLongRow) e = s;  // owned by segment CTAs
+        }
+        int trips = (e - s + kLanes - 1) / kLanes;
+#pragma unroll
+        for (int off = kLanes; off < 32; off <<= 1) {
+            const int other = __shfl_xor_sync(0xffffffffu, trips, off);
+            trips = other > trips ? other : trips;
+        }
+        const bool skip = row >= a.m || (a.rowPtr[row + 1] - a.rowPtr[row] > kLongRow);
+        for (int col0 = 0; col0 < a.n; col0 += kTileCols) {
             const int col = col0 + li * E;
             const bool colLive = col < a.n;
             float acc[E], comp[E];
 #pragma unroll
             for (int i = 0; i < E; ++i) acc[i] = comp[i] = 0.0f;
-            if (L == 32) RowDot<ValT, kKahan, 8>(a.colInd, a.val, a.B + col, a.ldb, s, e, L, colLive, acc, comp);
-            else RowDot<ValT, kKahan, 4>(a.colInd, a.val, a.B + col, a.ldb, s, e, L, colLive, acc, comp);
+            RowDot<ValT, kKahan, kLanes>(a.colInd, a.val, a.B + col, a.ldb, s, e, trips, colLive, acc, comp);
+            if (kKahan) {
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                if (kKahan) acc[i] -= comp[i];
-                for (int off = L; off < 32; off <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+                for (int i = 0; i < E; ++i) acc[i] -= comp[i];
             }
-            if (lane < L && colLive) StoreRowSlice<OutT, E>(a.C + row * a.ldc + col, acc, alpha, beta);
+            if (!skip && colLive) StoreRowSlice<OutT, E>(a.C + row * a.ldc + col, acc, alpha, beta);
         }
         return;
     }
 
-    // ---- one CTA per long-row segment ----
+    // ---- one CTA per long-row segment: the four warps take a quarter each ----
     const SegEntry seg = a.segs[blockIdx.x];
     const LongRow lr = a.longRows[seg.longIdx];
     const int rowStart = a.rowPtr[seg.row];
     const int rowEnd = a.rowPtr[seg.row + 1];
     const int segStart = rowStart + seg.seg * kSegNnz;
     const int segEnd = segStart + kSegNnz < rowEnd ? segStart + kSegNnz : rowEnd;
+    // inside a warp the lane groups take interleaved kLanes-wide chunks of the warp's quarter
     int ws = segStart + warp * kWarpSegNnz;
     int we = ws + kWarpSegNnz;
     if (ws > segEnd) ws = segEnd;
     if (we > segEnd) we = segEnd;
+    const int g = lane / kLanes;
     float *partial = a.partials + (long long)(lr.partBase + seg.seg) * a.n;
 
-    for (int col0 = 0; col0 < a.n; col0 += tileCols) {
+    for (int col0 = 0; col0 < a.n; col0 += kTileCols) {
         const int col = col0 + li * E;
         const bool colLive = col < a.n;
         float acc[E], comp[E];
 #pragma unroll
         for (int i = 0; i < E; ++i) acc[i] = comp[i] = 0.0f;
-        if (L == 32) RowDot<ValT, kKahan, 8>(a.colInd, a.val, a.B + col, a.ldb, ws, we, L, colLive, acc, comp);
-        else RowDot<ValT, kKahan, 4>(a.colInd, a.val, a.B + col, a.ldb, ws, we, L, colLive, acc, comp);
+        // group g walks chunks g, g + kRowsPerWarp, ... of [ws, we)
+        const int nChunks = (we - ws + kLanes - 1) / kLanes;
+        for (int ch0 = 0; ch0 < nChunks; ch0 += kRowsPerWarp) {  // same trip count in every group
+            const int ch = ch0 + g;
+            const int cs = ws + ch * kLanes < we ? ws + ch * kLanes : we;
+            const int ce = cs + kLanes < we ? cs + kLanes : we;
+            RowDot<ValT, kKahan, kLanes>(a.colInd, a.val, a.B + col, a.ldb, cs, ce, 1, colLive, acc, comp);
+        }
 #pragma unroll
         for (int i = 0; i < E; ++i) {
             if (kKahan) acc[i] -= comp[i];
-            for (int off = L; off < 32; off <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+#pragma unroll
+            for (int off = kLanes; off < 32; off <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
         }
-        if (lane < L) {
+        if (lane < kLanes) {
 #pragma unroll
             for (int i = 0; i < E; ++i) sAcc[warp][li * E + i] = acc[i];
         }
         __syncthreads();
         // warp 0 adds the four warps' slices in warp order
-        if (warp == 0 && lane < L && colLive) {
+        if (warp == 0 && lane < kLanes && colLive) {
             float tot[E];
 #pragma unroll
             for (int i = 0; i < E; ++i) {
@@ -412,20 +441,14 @@ __global__ void __launch_bounds__(256) SpmmGenericFloatKernel(const int32_t *__r
         float acc = 0.0f, comp = 0.0f;
         const int e = rowPtr[r + 1];
         for (int p = rowPtr[r]; p < e; ++p) {
-            const float prod = ToF32(val[p]) * ToF32(B[BIndex(g, colInd[p], j)]);
-            if (g.kahan) {
-                const float y = prod - comp;
-                const float t = acc + y;
-                comp = (t - acc) - y;
-                acc = t;
-            } else {
-                acc += prod;
-            }
+            const float b = ToF32(B[BIndex(g, colInd[p], j)]);
+            if (g.kahan) Accumulate<true>(ToF32(val[p]), b, acc, comp);
+            else Accumulate<false>(ToF32(val[p]), b, acc, comp);
         }
         if (g.kahan) acc -= comp;
         const long long ci = g.cRowMajor ? r * g.ldc + j : j * g.ldc + r;
-        float z = alpha * acc;
-        if (beta != 0.0f) z += beta * ToF32(C[ci]);
+        float z = __fmul_rn(alpha, acc);
+        if (beta != 0.0f) z = __fadd_rn(z, __fmul_rn(beta, ToF32(C[ci])));
         C[ci] = FromF32<OutT>(z);
     }
 }
@@ -502,11 +525,22 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
         a.partials = reinterpret_cast<float *>(p + L.offPartials);
         int lanes = 1;
         while (lanes < 32 && lanes * E < sh->n) lanes <<= 1;
-        a.lanesPerRow = lanes;
-        const long long blocks = (long long)segments + (sh->m + kWarps - 1) / kWarps;
+        const long long rowsPerBlock = (long long)kWarps * (32 / lanes);
+        const long long blocks = (long long)segments + (sh->m + rowsPerBlock - 1) / rowsPerBlock;
         if (blocks == 0) return 0;
-        if (sh->kahan) SpmmFastKernel<ValT, OutT, true><<<(unsigned)blocks, kThreads, 0, stream>>>(a);
-        else SpmmFastKernel<ValT, OutT, false><<<(unsigned)blocks, kThreads, 0, stream>>>(a);
+        const unsigned grid = (unsigned)blocks;
+        auto launch = [&]<int kLanes>() {
+            if (sh->kahan) SpmmFastKernel<ValT, OutT, true, kLanes><<<grid, kThreads, 0, stream>>>(a);
+            else SpmmFastKernel<ValT, OutT, false, kLanes><<<grid, kThreads, 0, stream>>>(a);
+        };
+        switch (lanes) {
+            case 1: launch.template operator()<1>(); break;
+            case 2: launch.template operator()<2>(); break;
+            case 4: launch.template operator()<4>(); break;
+            case 8: launch.template operator()<8>(); break;
+            case 16: launch.template operator()<16>(); break;
+            default: launch.template operator()<32>(); break;
+        }
         return (int)cudaGetLastError();
     }
     GenericShape g{sh->m, sh->n, sh->ldb, sh->ldc, sh->order_b == 0, sh->order_c == 0, sh->op_b, sh->kahan};

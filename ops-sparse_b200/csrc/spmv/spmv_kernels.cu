@@ -3,18 +3,19 @@
 // The reference's device code for this operator (sparse/spmv/arch22/kernels/spmv_kernel.h:
 // 27-310 non-transpose, 321-640 transpose) gives every core an equal count of rows and
 // walks them one at a time.  Here the work is cut by *merge path* instead: the rows' end
-// markers and the non-zeros form one merged sequence of rows + nnz items, every CTA takes
-// an equal slice (a tile) of it, streams its slice of col_ind / values with 128-bit
-// loads, gathers x, parks the products in shared memory and reduces them per row.  Inside
-// a tile rows are routed by length:
-//     short rows  -> a group of G lanes per row, G in {1,2,4,..,32} picked from the tile's
-//                    mean row length (G = 1 is scalar-row, G = 32 is warp-per-row);
-//     rows > 64   -> one warp per row (when G < 32);
-//     rows >= 1024 inside the tile -> the whole CTA reduces the row (vector-row).
-// A row cut by a tile boundary is finished without a second kernel and without waiting:
-// every tile that holds a piece of it stores its partial sum, then bumps an arrival
-// counter owned by the tile in which the row ends; whichever tile arrives last adds the
-// pieces in tile order (so the result does not depend on scheduling) and writes y.
+// markers and the non-zeros form one merged sequence of rows + nnz items and every CTA takes
+// an equal slice (a tile) of it, whatever the row lengths are.  A tile
+//   1. streams its slice of col_ind / values with 128-bit evict-first loads, gathers x
+//      through the read-only path and parks the products in shared memory;
+//   2. lets every thread walk 15 consecutive merge items (add a product, or close a row),
+//      then joins rows that span threads with a segmented scan over the threads' carries;
+//   3. writes y with one coalesced pass (alpha * sum + beta * y).
+// Short rows therefore cost a few instructions each (scalar-row work inside a thread), long
+// rows are summed by as many threads as they have items (vector-row), and a row cut by a
+// tile boundary is finished without a second kernel and without waiting: every tile that
+// holds a piece stores its partial sum, then bumps an arrival counter owned by the tile in
+// which the row ends; whichever tile arrives last adds the pieces in tile order (so the
+// result does not depend on scheduling) and writes y.
 //
 // Numerics follow the reference golden SpmvCpu (test/spmv/arch22/spmv_test.cpp:156-173):
 // values and x are widened to the compute type before the multiply, sums are kept in the
@@ -31,12 +32,10 @@
 namespace {
 
 constexpr int kTileThreads = 256;
-constexpr int kTileItems = 4092;   // merge items (row ends + non-zeros) per tile
-constexpr int kSmemWords = 4104;   // row offsets + products of one tile, with alignment slack
-constexpr int kLongRow = 64;       // rows longer than this leave the lane-group pass
-constexpr int kBlockRow = 1024;    // row pieces at least this long are reduced by the whole CTA
-constexpr int kMaxListB = 64;
-constexpr int kMaxListC = 8;
+constexpr int kItemsPerThread = 15;  // odd: consecutive threads start in different shared-memory banks
+constexpr int kTileItems = kTileThreads * kItemsPerThread;  // merge items (row ends + non-zeros) per tile
+constexpr int kSmemWords = kTileItems + 12;                 // row offsets + products, with alignment slack
+constexpr int kVecPerThread = (kTileItems + 6 + 4 * kTileThreads - 1) / (4 * kTileThreads);
 
 inline size_t AlignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -164,13 +163,16 @@ struct TileArgs {
 template <typename CompT, typename ValT, typename OutT, bool kVec>
 __global__ void __launch_bounds__(kTileThreads) SpmvTileKernel(const TileArgs<CompT, ValT, OutT> a)
 {
-    __shared__ __align__(16) int32_t smem[kSmemWords];
-    __shared__ int32_t listB[kMaxListB];
-    __shared__ int32_t listC[kMaxListC];
-    __shared__ int32_t listCount[2];
-    __shared__ CompT warpSum[kTileThreads / 32];
+    __shared__ __align__(16) int32_t smem[kSmemWords];   // row offsets, then products
+    __shared__ CompT sRowSum[kTileItems];                // finished sum of every row that ends here
+    __shared__ CompT sScan[kTileThreads];                // per-thread carry after the segmented scan
+    __shared__ int32_t sWarpKeyFirst[kTileThreads / 32];
+    __shared__ int32_t sWarpKeyLast[kTileThreads / 32];
+    __shared__ CompT sWarpValLast[kTileThreads / 32];
 
     const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
     const int t = blockIdx.x;
     const int i0 = a.tileRow[t];
     const int i1 = a.tileRow[t + 1];
@@ -187,16 +189,15 @@ __global__ void __launch_bounds__(kTileThreads) SpmvTileKernel(const TileArgs<Co
     CompT *sProd = reinterpret_cast<CompT *>(smem + prodOff);
     const int base = j0 & ~3;    // products are stored at sProd[index - base]
 
-    if (tid < 2) listCount[tid] = 0;
     for (int k = tid; k <= R; k += kTileThreads) sRow[k] = a.rowPtr[i0 + k];
 
     // ---- phase 1: stream the tile's non-zeros, gather x, store products -------------
     if (kVec) {
-        const int nvec = (j1 - base + 3) >> 2;  // <= 1024
-        int4 c[4];
-        Quad<ValT> v[4];
+        const int nvec = (j1 - base + 3) >> 2;  // <= kVecPerThread * kTileThreads
+        int4 c[kVecPerThread];
+        Quad<ValT> v[kVecPerThread];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kVecPerThread; ++u) {
             const int q = tid + u * kTileThreads;
             const int idx = base + 4 * q;
             c[u] = make_int4(0, 0, 0, 0);
@@ -220,21 +221,20 @@ __global__ void __launch_bounds__(kTileThreads) SpmvTileKernel(const TileArgs<Co
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kVecPerThread; ++u) {
             const int q = tid + u * kTileThreads;
             if (q < nvec) {
                 const int idx = base + 4 * q;
                 const int cc[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
-                CompT p[4];
+                alignas(16) CompT p[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    // Entries outside [0, nnz) were zero-filled above (column 0, value 0).
+                    // Entries past the end of the arrays were zero-filled above (column 0, value 0).
                     const bool live = idx + e < a.nnz;
                     const ValT xv = live ? __ldg(a.x + cc[e]) : ValT(0);
                     p[e] = Widen<CompT>(v[u].v[e]) * Widen<CompT>(xv);
                 }
-                CompT *dst = sProd + 4 * q;
-                dst[0] = p[0]; dst[1] = p[1]; dst[2] = p[2]; dst[3] = p[3];
+                *reinterpret_cast<int4 *>(sProd + 4 * q) = *reinterpret_cast<const int4 *>(p);
             }
         }
     } else {
@@ -245,10 +245,74 @@ __global__ void __launch_bounds__(kTileThreads) SpmvTileKernel(const TileArgs<Co
     }
     __syncthreads();
 
+    // ---- phase 2: every thread walks kItemsPerThread consecutive merge items -----------
+    // Local merge coordinates: row ends sRow[k + 1] - j0 (k < R) against non-zero indices 0..nn-1.
+    const int items = R + nn;
+    const int dBeg = tid * kItemsPerThread < items ? tid * kItemsPerThread : items;
+    const int dEnd = dBeg + kItemsPerThread < items ? dBeg + kItemsPerThread : items;
+    int rowIdx, nzIdx;
+    {
+        int lo = dBeg - nn > 0 ? dBeg - nn : 0;
+        int hi = dBeg < R ? dBeg : R;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (sRow[mid + 1] - j0 <= dBeg - mid - 1) lo = mid + 1;
+            else hi = mid;
+        }
+        rowIdx = lo;
+        nzIdx = dBeg - lo;
+    }
+    const CompT *prod = sProd + (j0 - base);
+    int rowEnd = rowIdx < R ? sRow[rowIdx + 1] - j0 : 0x7fffffff;
+    CompT running = CompT(0);
+    int firstEnded = -1;  // first row this thread finishes: it may have begun in an earlier thread
+#pragma unroll
+    for (int it = 0; it < kItemsPerThread; ++it) {
+        if (dBeg + it < dEnd) {
+            if (nzIdx < rowEnd) {
+                running += prod[nzIdx];
+                ++nzIdx;
+            } else {
+                sRowSum[rowIdx] = running;
+                if (firstEnded < 0) firstEnded = rowIdx;
+                running = CompT(0);
+                ++rowIdx;
+                rowEnd = rowIdx < R ? sRow[rowIdx + 1] - j0 : 0x7fffffff;
+            }
+        }
+    }
+
+    // Segmented inclusive scan of the (row, partial) carries over the threads of the CTA: after
+    // it, thread u holds the sum of the pieces of its last row held by threads <= u.
+    CompT scan = running;
+    const int key = rowIdx;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const CompT v2 = __shfl_up_sync(0xffffffffu, scan, off);
+        const int k2 = __shfl_up_sync(0xffffffffu, key, off);
+        if (lane >= off && k2 == key) scan += v2;
+    }
+    if (lane == 0) sWarpKeyFirst[warp] = key;
+    if (lane == 31) {
+        sWarpKeyLast[warp] = key;
+        sWarpValLast[warp] = scan;
+    }
+    __syncthreads();
+    if (__shfl_sync(0xffffffffu, key, 0) == key) {  // this thread's run reaches the start of its warp
+        for (int w = warp - 1; w >= 0; --w) {
+            if (sWarpKeyLast[w] != key) break;
+            scan += sWarpValLast[w];
+            if (sWarpKeyFirst[w] != key) break;
+        }
+    }
+    sScan[tid] = scan;
+    __syncthreads();
+    if (firstEnded >= 0 && tid > 0) sRowSum[firstEnded] += sScan[tid - 1];
+    __syncthreads();
+
+    // ---- phase 3: coalesced epilogue ---------------------------------------------------
     const CompT alpha = a.sc.Alpha();
     const CompT beta = a.sc.Beta();
-
-    // Writes the finished value of row r.
     auto storeRow = [&](int r, CompT sum) {
         CompT z = alpha * sum;
         if (beta != CompT(0)) z += beta * Widen<CompT>(a.y[r]);
@@ -269,85 +333,23 @@ __global__ void __launch_bounds__(kTileThreads) SpmvTileKernel(const TileArgs<Co
             storeRow(r, s);
         }
     };
-    // Routes the sum of local row k (k == R is the piece of the row that continues in the next tile).
-    auto emit = [&](int k, CompT sum) {
-        if (k == R) {
-            a.partTail[t] = sum;
-            const int t1 = (int)(((long long)i1 + a.rowPtr[i1 + 1]) / kTileItems);
-            arrive(i1, t1);
-        } else if (k == 0 && sRow[0] < j0) {
-            a.partHead[t] = sum;
+    const bool headContinues = R > 0 && sRow[0] < j0;  // row i0 began in an earlier tile
+    for (int k = tid; k < R; k += kTileThreads) {
+        if (k == 0 && headContinues) {
+            a.partHead[t] = sRowSum[0];
             arrive(i0, t);
         } else {
-            storeRow(i0 + k, sum);
+            storeRow(i0 + k, sRowSum[k]);
         }
-    };
-
+    }
     // Piece of the row after the last complete one, if this tile holds any of it.
-    const int tailStart = sRow[R] > j0 ? sRow[R] : j0;
-    const bool hasTail = (i1 < a.rows) && (j1 > tailStart);
-    const int nLocal = R + (hasTail ? 1 : 0);
-
-    // ---- phase 2: per-row reduction, routed by row length ---------------------------
-    int G = 1;
-    {
-        const int avg = nn / (R > 0 ? R : 1);
-        while (G < 32 && G < avg) G <<= 1;
-    }
-    const int groups = kTileThreads / G;
-    const int lane = tid & (G - 1);
-    for (int kb = 0; kb < nLocal; kb += groups) {  // uniform trip count: shuffles below need whole warps
-        const int k = kb + tid / G;
-        CompT sum = CompT(0);
-        bool mine = false;
-        if (k < nLocal) {
-            const int s = (sRow[k] > j0 ? sRow[k] : j0) - base;
-            const int e = (k == R ? j1 : sRow[k + 1]) - base;
-            const int len = e - s;
-            if (len >= kBlockRow) {
-                if (lane == 0) listC[atomicAdd(&listCount[1], 1)] = k;
-            } else if (G < 32 && len > kLongRow) {
-                if (lane == 0) listB[atomicAdd(&listCount[0], 1)] = k;
-            } else {
-                mine = true;
-                for (int p = s + lane; p < e; p += G) sum += sProd[p];
-            }
+    if (tid == kTileThreads - 1) {
+        const int tailStart = sRow[R] > j0 ? sRow[R] : j0;
+        if (i1 < a.rows && j1 > tailStart) {
+            a.partTail[t] = scan;  // key == R here: the run of carries that ends the tile
+            const int t1 = (int)(((long long)i1 + a.rowPtr[i1 + 1]) / kTileItems);
+            arrive(i1, t1);
         }
-        sum = GroupSum(sum, G);
-        if (mine && lane == 0) emit(k, sum);
-    }
-    __syncthreads();
-
-    // rows of 65..1023 entries: one warp per row
-    const int nB = listCount[0];
-    for (int w = tid >> 5; w < nB; w += kTileThreads / 32) {
-        const int k = listB[w];
-        const int s = (sRow[k] > j0 ? sRow[k] : j0) - base;
-        const int e = (k == R ? j1 : sRow[k + 1]) - base;
-        CompT sum = CompT(0);
-        for (int p = s + (tid & 31); p < e; p += 32) sum += sProd[p];
-        sum = GroupSum(sum, 32);
-        if ((tid & 31) == 0) emit(k, sum);
-    }
-
-    // row pieces of >= 1024 entries: the whole CTA per row
-    const int nC = listCount[1];
-    for (int w = 0; w < nC; ++w) {
-        const int k = listC[w];
-        const int s = (sRow[k] > j0 ? sRow[k] : j0) - base;
-        const int e = (k == R ? j1 : sRow[k + 1]) - base;
-        CompT sum = CompT(0);
-        for (int p = s + tid; p < e; p += kTileThreads) sum += sProd[p];
-        sum = GroupSum(sum, 32);
-        if ((tid & 31) == 0) warpSum[tid >> 5] = sum;
-        __syncthreads();
-        if (tid == 0) {
-            CompT tot = CompT(0);
-#pragma unroll
-            for (int q = 0; q < kTileThreads / 32; ++q) tot += warpSum[q];
-            emit(k, tot);
-        }
-        __syncthreads();
     }
 }
 

@@ -111,6 +111,24 @@ def test_widths_and_types(handle, device, oracle, vt, ot, n):
     check_compact(oracle, rp, ci, val, B, C, vt, ot, 1.5, -0.5, got, f"{vt}->{ot} n={n}")
 
 
+@pytest.mark.parametrize("vt,ot,n", [("f32", "f32", 64), ("f32", "f32", 8), ("f32", "f32", 200), ("bf16", "f32", 256),
+                                     ("bf16", "bf16", 64), ("f16", "f16", 40)])
+def test_bit_identical_to_golden_for_rows_up_to_1024(handle, device, oracle, vt, ot, n):
+    """Rows of at most 1024 entries are summed in CSR order with unfused multiply-add: same bits as the golden."""
+    rng = np.random.default_rng(n + len(vt))
+    m, k = 500, 3000
+    lengths = rng.integers(0, 70, size=m)
+    lengths[7], lengths[77], lengths[400] = 1024, 1000, 0
+    rp, ci, val, B, C = compact_case(oracle, rng, m, k, n, lengths, vt, ot, 1.25, 0.5)
+    got = run_spmm(handle, device, rp, ci, val, vt, B, C, ot, m, k, n, n, n, 1.25, 0.5)
+    if vt == "f32":
+        gold = oracle.spmm_f32_layout(m, n, rp, ci, val, B, n, True, False, C, n, True, 1.25, 0.5).reshape(m, n)
+        assert np.array_equal(got.view(np.uint32), gold.view(np.uint32))
+    else:
+        gold = oracle.spmm_16(rp, ci, val, B, C, 1.25, 0.5, vt, ot)
+        assert np.array_equal(got.view(np.uint8), gold.view(np.uint8))
+
+
 def test_long_rows_segments(handle, device, oracle):
     """Rows of 1024, 1025, 4096, 4097, 9000 and 20000 entries next to short ones."""
     rng = np.random.default_rng(11)
@@ -225,6 +243,7 @@ def test_golden_fixtures_spmm35(handle, device, oracle, golden_dir):
                        c_order="col" if ccol else "row", alg=1)
         ok, st = oracle.verify_mere_mare(got, z[f"{name}/gold"], m, n, ldc, not ccol)
         assert ok, (name, st)
+        assert np.array_equal(got.ravel().view(np.uint32), z[f"{name}/gold"].view(np.uint32)), name  # every layout
     z = np.load(golden_dir / "spmm35_f16_i8.npz")
     m, k, n = (int(v) for v in z["shape"])
     got = run_spmm(handle, device, z["row_ptr"], z["col_ind"], z["f16_val"], "f16", z["f16_B"],
@@ -232,6 +251,7 @@ def test_golden_fixtures_spmm35(handle, device, oracle, golden_dir):
     ok, st = oracle.verify_mere_mare(oracle.from_storage(got, "f16"), oracle.from_storage(z["f16_gold"], "f16"), m, n, n,
                                      True, 2.0 ** -10, 10 * 2.0 ** -10)
     assert ok, st
+    assert np.array_equal(got.ravel(), z["f16_gold"])
     got = run_spmm(handle, device, z["row_ptr"], z["col_ind"], z["i8_val"], "i8", z["i8_B"],
                    np.zeros(m * n, np.int32), "i32", m, k, n, n, n, 1, 0)
     assert np.array_equal(got.ravel(), z["i8_gold"])
