@@ -39,6 +39,9 @@ def test_reference_spmm_arch35_harness(built, device):
     assert "Overall: PASS" in out
 
 
+@pytest.mark.skipif(os.environ.get("B200SP_RUN_SLOW_HARNESS") != "1",
+                    reason="the arch22 harness spends about 8 minutes in its own CPU golden loops (200 cases x 10 "
+                           "timed repetitions); set B200SP_RUN_SLOW_HARNESS=1 to run it")
 def test_reference_spmm_arch22_harness(built, device):
     out = run("spmm22_test", 1500)
     assert "Total: 0 failed" in out
