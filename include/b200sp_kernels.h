@@ -72,6 +72,35 @@ int b200sp_spmv_trans_launch(const int32_t *row_ptr, const int32_t *col_ind, con
                              int comp_type, int val_type, int out_type, void *scratch, size_t scratch_bytes,
                              void *stream);
 
+/* Largest rows + nnz that b200sp_spmv_f32_noalloc accepts. */
+#define B200SP_NOALLOC_MAX_ITEMS (1LL << 26)
+
+/* y = alpha * A * x + beta * y for fp32 CSR, for callers that must not allocate device memory.
+ * (No counterpart in the reference: its SpMV takes whatever workspace it needs from the handle.)
+ *
+ * Some callers cannot reach cudaMalloc at the moment they need a product: code that runs inside
+ * a framework whose caching allocator owns all device memory and hands none back, a solver
+ * loop whose memory was sized and frozen at start-up, a plug-in that is only given pointers.
+ * The regular path needs a workspace from them (aclsparseSpMVGetBufferSize) or takes the 4 MiB
+ * the handle allocated in aclsparseCreate.  This entry point needs neither a handle nor a buffer:
+ * the tile table, arrival counters and partial sums live in an array that is part of the
+ * library image in device memory (about 0.3 MB on every GPU that loads the library, held until
+ * the process exits).  It calls no cudaMalloc / cudaFree and no routine that allocates.
+ *
+ * Limits and rules:
+ *  - rows + nnz <= B200SP_NOALLOC_MAX_ITEMS; a larger matrix is refused with cudaErrorInvalidValue
+ *    and a message on stderr, nothing is launched.
+ *  - The first call on each device looks up the array's device address (one runtime query, with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - Every call on a device uses the same array and rewrites it (the tile table is rebuilt and
+ *    the counters are zeroed at the start of each call, so stale contents never matter).  Two
+ *    calls that can overlap on the GPU -- different streams, or different host threads -- race on
+ *    it: keep the calls of one device in one stream, or order them with events.
+ *  - All pointers are device pointers; 16-byte aligned col_ind / val take the vector-load kernel. */
+int b200sp_spmv_f32_noalloc(const int32_t *row_ptr, const int32_t *col_ind, const float *val, const float *x,
+                            float *y, int64_t rows, int64_t cols, int64_t nnz, float alpha, float beta,
+                            void *stream);
+
 /* ------------------------------------------------------------------ SpMM ------------- */
 
 /* Dense operand layout, same meaning as the reference's SpmmTilingData

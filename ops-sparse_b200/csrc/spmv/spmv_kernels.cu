@@ -22,6 +22,7 @@
 // compute type, the result is alpha*sum + beta*y rounded once to the output type.
 // beta == 0 never reads y.
 #include <cstdint>
+#include <cstdio>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -598,3 +599,66 @@ int b200sp_spmv_trans_launch(const int32_t *row_ptr, const int32_t *col_ind, con
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- entry point without allocation
+
+namespace {
+
+// Scratch for b200sp_spmv_f32_noalloc: the tile table, arrival counters and partial sums that
+// b200sp_spmv_analyze would otherwise write into a caller-allocated workspace.  Every GPU that
+// loads the library carries this array until the process exits.
+constexpr int64_t kNoAllocMaxItems = B200SP_NOALLOC_MAX_ITEMS;
+constexpr size_t kNoAllocBytes = 16 * ((size_t)(kNoAllocMaxItems / kTileItems) + 2) + 4 * 256;
+static __device__ __align__(256) unsigned char gNoAllocScratch[kNoAllocBytes];
+
+constexpr int kMaxDevices = 64;
+void *gNoAllocAddr[kMaxDevices] = {};  // device address of gNoAllocScratch, per device ordinal
+
+// In host code `gNoAllocScratch` is only a handle for the runtime, not an address a kernel can
+// use; the device address has to be asked for, once per device, with that device current.
+int NoAllocScratchAddress(void **out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    if (gNoAllocAddr[dev] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, gNoAllocScratch);
+        if (e != cudaSuccess) return (int)e;
+        gNoAllocAddr[dev] = p;
+    }
+    *out = gNoAllocAddr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int b200sp_spmv_f32_noalloc(const int32_t *row_ptr, const int32_t *col_ind, const float *val,
+                                       const float *x, float *y, int64_t rows, int64_t cols, int64_t nnz,
+                                       float alpha, float beta, void *stream)
+{
+    (void)cols;
+    if (rows < 0 || nnz < 0 || rows > INT32_MAX || nnz > INT32_MAX) return (int)cudaErrorInvalidValue;
+    const PlanLayout L = LayoutFor(rows, nnz);
+    if (rows + nnz > kNoAllocMaxItems || L.total > kNoAllocBytes) {
+        std::fprintf(stderr,
+                     "b200sp_spmv_f32_noalloc: rows + nnz = %lld exceeds B200SP_NOALLOC_MAX_ITEMS = %lld; "
+                     "use aclsparseSpMV with a caller-provided buffer for a matrix of this size\n",
+                     (long long)(rows + nnz), (long long)kNoAllocMaxItems);
+        return (int)cudaErrorInvalidValue;
+    }
+    void *scratch = nullptr;
+    const int rc = NoAllocScratchAddress(&scratch);
+    if (rc != 0) return rc;
+    if (L.ntiles == 0) return 0;
+    // The analysis rewrites the tile table and zeroes the arrival counters, so nothing a previous
+    // call left in the array is read.
+    const int an = b200sp_spmv_analyze(row_ptr, rows, nnz, scratch, kNoAllocBytes, stream);
+    if (an != 0) return an;
+    b200spScalars sc{};
+    sc.alpha_f = alpha;
+    sc.beta_f = beta;
+    return LaunchTyped<float, float, float>(row_ptr, col_ind, val, x, y, rows, nnz, &sc, scratch,
+                                            static_cast<cudaStream_t>(stream));
+}
