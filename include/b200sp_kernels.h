@@ -47,22 +47,30 @@ typedef struct b200spScalars {
 
 /* ------------------------------------------------------------------ SpMV ------------- */
 
-/* Bytes of workspace the SpMV analysis needs for a rows x * matrix with nnz entries. */
-size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t nnz);
+/* Bytes of workspace the SpMV analysis needs for a rows x cols matrix with nnz entries whose
+ * values (and x) have element type val_type. */
+size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t cols, int64_t nnz, int val_type);
 
-/* Analysis pass: splits the merged (row-end, nnz) sequence of the CSR matrix into
- * equal tiles and writes the tile table plus zeroed arrival counters into `plan`.
+/* Analysis pass.  Always: splits the merged (row-end, nnz) sequence of the CSR matrix into equal
+ * tiles and writes the tile table plus zeroed arrival counters into `plan`.
+ * With long_rows != NULL it also routes rows of 1024 or more entries to the long-row kernel
+ * (x staged in shared memory by column block): it lists them, checks that their column indices
+ * ascend, cuts them at the column-block borders, then synchronises `stream` once to report
+ * how many there are in *long_rows (0 when the matrix has none, when one of them is unsorted, or
+ * when the matrix is too wide for the scheme).  With long_rows == NULL (col_ind may be NULL too)
+ * nothing synchronises and every row stays in the tiles.
  * Returns cudaErrorInvalidValue when plan_bytes is too small. */
-int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void *plan, size_t plan_bytes,
-                        void *stream);
+int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols, int64_t nnz,
+                        int val_type, void *plan, size_t plan_bytes, int32_t *long_rows, void *stream);
 
 /* y = alpha * A * x + beta * y, A in CSR with int32 zero-based indices.
  * comp_type is B200SP_F32 or B200SP_I32; x has val_type; y has out_type.
- * `plan` must have been filled by b200sp_spmv_analyze for the same row_ptr / rows / nnz.
+ * `plan` / `long_rows` come from b200sp_spmv_analyze for the same row_ptr / col_ind / shape
+ * (long_rows = 0 if it was called with long_rows == NULL).
  * With plan == NULL a row-group kernel that needs no workspace is used. */
 int b200sp_spmv_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *x, void *y,
                        int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars, int comp_type,
-                       int val_type, int out_type, void *plan, void *stream);
+                       int val_type, int out_type, void *plan, int32_t long_rows, void *stream);
 
 /* y = alpha * A^T * x + beta * y (y has `cols` entries).  First scales y by beta, then
  * scatters alpha * x[i] * a_ij into y[j] with atomic adds.  For 16-bit y an fp32
@@ -136,6 +144,12 @@ int b200sp_spmm_launch(const int32_t *row_ptr, const int32_t *col_ind, const voi
 
 /* Number of streaming multiprocessors of the current device (cached after the first call). */
 int b200sp_sm_count(void);
+
+/* Kernels this library has launched in the calling process so far (every analysis, SpMV and SpMM
+ * kernel counts one).  A benchmark reads it before and after a timed region. */
+unsigned long long b200sp_kernel_launches(void);
+/* Used by the library's own launch sites to keep that count. */
+void b200sp_note_launches(int n);
 
 #ifdef __cplusplus
 }

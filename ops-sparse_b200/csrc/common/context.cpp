@@ -1,6 +1,7 @@
 // aclsparse handle: stream, pointer mode and workspace management.
 // Behaviour follows sparse/common/aclsparse_auxiliary.cpp:64-198, 253-279 of the reference;
 // device memory comes from the CUDA runtime instead of aclrtMalloc.
+#include <atomic>
 #include <new>
 
 #include "internal.h"
@@ -18,7 +19,14 @@ int LogLevel()
 
 }  // namespace b200sp
 
+namespace {
+std::atomic<unsigned long long> gKernelLaunches{0};
+}
+
 extern "C" {
+
+unsigned long long b200sp_kernel_launches(void) { return gKernelLaunches.load(std::memory_order_relaxed); }
+void b200sp_note_launches(int n) { gKernelLaunches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 aclsparseStatus_t aclsparseCreate(aclsparseHandle_t *handle)
 {

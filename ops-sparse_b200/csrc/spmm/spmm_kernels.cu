@@ -36,7 +36,10 @@
 
 namespace {
 
-constexpr int kThreads = 128;           // 4 warps: 4 rows, or one long-row segment
+#ifndef B200SP_SPMM_THREADS
+#define B200SP_SPMM_THREADS 128
+#endif
+constexpr int kThreads = B200SP_SPMM_THREADS;  // warps of a CTA: one lane-group set each, or one long-row segment
 constexpr int kWarps = kThreads / 32;
 constexpr int kLongRow = 1024;          // rows longer than this are handled by segment CTAs
 constexpr int kSegNnz = 4096;           // non-zeros per segment
@@ -207,22 +210,47 @@ __device__ __forceinline__ void Accumulate(float v, float b, float &acc, float &
 // Adds sum_{p in [s, e)} val[p] * B[col[p], slice] to acc, p ascending.  The kLanes lanes of a
 // group call it together with the same s, e (groups of one warp may differ); `trips` is the
 // warp-uniform number of kLanes-wide chunks to walk (>= this group's own need).
+#ifndef B200SP_SPMM_BATCH
+#define B200SP_SPMM_BATCH 8
+#endif
+
 template <typename ValT, bool kKahan, int kLanes>
 __device__ __forceinline__ void RowDot(const int32_t *__restrict__ colInd, const ValT *__restrict__ val,
                                        const ValT *__restrict__ Bslice, long long ldb, int s, int e, int trips,
-                                       bool colLive, float (&acc)[Pack<ValT>::kElems],
+                                       bool colLive, bool allColsLive, float (&acc)[Pack<ValT>::kElems],
                                        float (&comp)[Pack<ValT>::kElems])
 {
     constexpr int E = Pack<ValT>::kElems;
-    constexpr int kBatch = kLanes < 8 ? kLanes : 8;  // B rows in flight per lane
+    constexpr int kBatch = kLanes < B200SP_SPMM_BATCH ? kLanes : B200SP_SPMM_BATCH;  // B rows in flight per lane
     const int li = threadIdx.x & (kLanes - 1);
     for (int chunk = 0; chunk < trips; ++chunk) {
         const int p0 = s + chunk * kLanes;
+        const int rem = e - p0;  // entries of this group's row left; <= 0 once the row is done
         int myCol = 0;
         float myVal = 0.0f;
-        if (p0 + li < e) {
+        if (li < rem) {
             myCol = __ldcs(colInd + p0 + li);
             myVal = ToF32(__ldcs(val + p0 + li));
+        }
+        // Whole warp on full chunks and live columns: straight-line code without predicates.
+        if (allColsLive && __all_sync(0xffffffffu, rem >= kLanes)) {
+#pragma unroll
+            for (int q0 = 0; q0 < kLanes; q0 += kBatch) {
+                float b[kBatch][E];
+                float v[kBatch];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int c = __shfl_sync(0xffffffffu, myCol, q0 + u, kLanes);
+                    v[u] = __shfl_sync(0xffffffffu, myVal, q0 + u, kLanes);
+                    Pack<ValT>::Load(Bslice + (long long)c * ldb, b[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+#pragma unroll
+                    for (int i = 0; i < E; ++i) Accumulate<kKahan>(v[u], b[u][i], acc[i], comp[i]);
+                }
+            }
+            continue;
         }
 #pragma unroll
         for (int q0 = 0; q0 < kLanes; q0 += kBatch) {
@@ -233,7 +261,7 @@ __device__ __forceinline__ void RowDot(const int32_t *__restrict__ colInd, const
             for (int u = 0; u < kBatch; ++u) {
                 const int c = __shfl_sync(0xffffffffu, myCol, q0 + u, kLanes);
                 v[u] = __shfl_sync(0xffffffffu, myVal, q0 + u, kLanes);
-                live[u] = colLive && (p0 + q0 + u < e);
+                live[u] = colLive && (q0 + u < rem);
                 if (live[u]) {
                     Pack<ValT>::Load(Bslice + (long long)c * ldb, b[u]);
                 } else {
@@ -313,10 +341,11 @@ __global__ void __launch_bounds__(kThreads) SpmmFastKernel(const FastArgs<ValT, 
         for (int col0 = 0; col0 < a.n; col0 += kTileCols) {
             const int col = col0 + li * E;
             const bool colLive = col < a.n;
+            const bool allLive = col0 + kTileCols <= a.n;
             float acc[E], comp[E];
 #pragma unroll
             for (int i = 0; i < E; ++i) acc[i] = comp[i] = 0.0f;
-            RowDot<ValT, kKahan, kLanes>(a.colInd, a.val, a.B + col, a.ldb, s, e, trips, colLive, acc, comp);
+            RowDot<ValT, kKahan, kLanes>(a.colInd, a.val, a.B + col, a.ldb, s, e, trips, colLive, allLive, acc, comp);
             if (kKahan) {
 #pragma unroll
                 for (int i = 0; i < E; ++i) acc[i] -= comp[i];
@@ -344,6 +373,7 @@ __global__ void __launch_bounds__(kThreads) SpmmFastKernel(const FastArgs<ValT, 
     for (int col0 = 0; col0 < a.n; col0 += kTileCols) {
         const int col = col0 + li * E;
         const bool colLive = col < a.n;
+        const bool allLive = col0 + kTileCols <= a.n;
         float acc[E], comp[E];
 #pragma unroll
         for (int i = 0; i < E; ++i) acc[i] = comp[i] = 0.0f;
@@ -353,7 +383,7 @@ __global__ void __launch_bounds__(kThreads) SpmmFastKernel(const FastArgs<ValT, 
             const int ch = ch0 + g;
             const int cs = ws + ch * kLanes < we ? ws + ch * kLanes : we;
             const int ce = cs + kLanes < we ? cs + kLanes : we;
-            RowDot<ValT, kKahan, kLanes>(a.colInd, a.val, a.B + col, a.ldb, cs, ce, 1, colLive, acc, comp);
+            RowDot<ValT, kKahan, kLanes>(a.colInd, a.val, a.B + col, a.ldb, cs, ce, 1, colLive, allLive, acc, comp);
         }
 #pragma unroll
         for (int i = 0; i < E; ++i) {
@@ -532,6 +562,7 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
         auto launch = [&]<int kLanes>() {
             if (sh->kahan) SpmmFastKernel<ValT, OutT, true, kLanes><<<grid, kThreads, 0, stream>>>(a);
             else SpmmFastKernel<ValT, OutT, false, kLanes><<<grid, kThreads, 0, stream>>>(a);
+            b200sp_note_launches(1);
         };
         switch (lanes) {
             case 1: launch.template operator()<1>(); break;
@@ -551,6 +582,7 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
     SpmmGenericFloatKernel<ValT, OutT><<<(unsigned)(want < cap ? want : cap), 256, 0, stream>>>(
         rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(B), static_cast<OutT *>(C), g,
         MakeF(s));
+    b200sp_note_launches(1);
     return (int)cudaGetLastError();
 }
 
@@ -576,6 +608,7 @@ int b200sp_spmm_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, int64
             row_ptr, (int)rows, reinterpret_cast<int32_t *>(p + L.offCounts),
             reinterpret_cast<LongRow *>(p + L.offLong), reinterpret_cast<SegEntry *>(p + L.offSegs),
             reinterpret_cast<int32_t *>(p + L.offCounters));
+        b200sp_note_launches(1);
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
@@ -612,6 +645,7 @@ int b200sp_spmm_launch(const int32_t *row_ptr, const int32_t *col_ind, const voi
         SpmmGenericInt8Kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
             row_ptr, col_ind, static_cast<const int8_t *>(val), static_cast<const int8_t *>(B),
             static_cast<int32_t *>(C), g, MakeI(scalars));
+        b200sp_note_launches(1);
         return (int)cudaGetLastError();
     }
     return (int)cudaErrorInvalidValue;

@@ -155,6 +155,37 @@ def test_every_row_length_0_to_130(handle, device, oracle):
         check_against_oracle(oracle, rp, ci, val, x, y, -0.75, 2.0, "f32", "f32", got, what=f"lengths/{mode}")
 
 
+@pytest.mark.parametrize("vt,ot", [("f32", "f32"), ("f16", "f32"), ("bf16", "bf16"), ("i32", "i32")])
+def test_long_rows_take_the_column_blocked_kernel(handle, device, oracle, vt, ot):
+    """Rows of 1024+ entries spread over several 128 KB blocks of x, next to short rows and seams."""
+    rng = np.random.default_rng(21)
+    M, N = 3000, 150000
+    lengths = rng.integers(0, 12, size=M)
+    for r, L in zip((0, 7, 500, 501, 1999, 2999), (1024, 1023, 1500, 5000, 20000, 60000)):
+        lengths[r] = L
+    rp, ci = random_csr(rng, M, N, lengths)
+    val, x, y = draw(rng, oracle, rp[-1], vt), draw(rng, oracle, N, vt), draw(rng, oracle, M, ot)
+    a, b = (2, -1) if ot == "i32" else (1.5, 0.5)
+    for mode in ("plan", "workspace"):  # Preprocess routes long rows away; the per-call analysis does not
+        got = run_spmv(handle, device, oracle, rp, ci, val, x, y, a, b, vt, ot, rows=M, cols=N, mode=mode)
+        check_against_oracle(oracle, rp, ci, val, x, y, a, b, vt, ot, got, cols=N, what=f"long rows {vt}/{mode}")
+
+
+def test_unsorted_long_row_stays_in_the_tiles(handle, device, oracle):
+    """The column-block cut needs ascending columns; a long row without them must still be summed right."""
+    rng = np.random.default_rng(22)
+    M, N = 500, 90000
+    lengths = rng.integers(0, 20, size=M)
+    lengths[100], lengths[300] = 6000, 3000
+    rp, ci = random_csr(rng, M, N, lengths)
+    seg = ci[rp[100]:rp[101]].copy()
+    rng.shuffle(seg)
+    ci[rp[100]:rp[101]] = seg
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    got = run_spmv(handle, device, oracle, rp, ci, val, x, y, 1.0, 1.0, "f32", "f32", rows=M, cols=N)
+    check_against_oracle(oracle, rp, ci, val, x, y, 1.0, 1.0, "f32", "f32", got, cols=N, what="unsorted long row")
+
+
 @pytest.mark.parametrize("shape", ["all_empty", "one_row_huge", "many_empty_then_long", "single_entry", "tall_thin"])
 def test_edge_shapes(handle, device, oracle, shape):
     rng = np.random.default_rng(7)
