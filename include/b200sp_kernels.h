@@ -47,30 +47,33 @@ typedef struct b200spScalars {
 
 /* ------------------------------------------------------------------ SpMV ------------- */
 
-/* Bytes of workspace the SpMV analysis needs for a rows x cols matrix with nnz entries whose
- * values (and x) have element type val_type. */
-size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t cols, int64_t nnz, int val_type);
+/* Bytes of workspace the SpMV analysis needs for a rows x * matrix with nnz entries
+ * (enough for either kind of plan below). */
+size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t nnz);
+/* Bytes a tile plan alone needs (what a per-call analysis with plan_info == NULL writes). */
+size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz);
 
-/* Analysis pass.  Always: splits the merged (row-end, nnz) sequence of the CSR matrix into equal
- * tiles and writes the tile table plus zeroed arrival counters into `plan`.
- * With long_rows != NULL it also routes rows of 1024 or more entries to the long-row kernel
- * (x staged in shared memory by column block): it lists them, checks that their column indices
- * ascend, cuts them at the column-block borders, then synchronises `stream` once to report
- * how many there are in *long_rows (0 when the matrix has none, when one of them is unsorted, or
- * when the matrix is too wide for the scheme).  With long_rows == NULL (col_ind may be NULL too)
- * nothing synchronises and every row stays in the tiles.
+/* Analysis pass, two kinds:
+ *  plan_info == NULL : tile plan.  Splits the merged (row-end, nnz) sequence of the CSR matrix into
+ *      equal tiles and writes the tile table plus zeroed arrival counters into `plan`.  Nothing
+ *      synchronises.  b200sp_spmv_launch then runs the merge-path tile kernel.
+ *  plan_info != NULL : binned plan (4 ints are written to it: kind = 1, medium rows, long rows,
+ *      lane-group width).  Rows are binned by length -- short (<= 32 entries), medium, long (>= 1024)
+ *      -- the medium and long rows are listed in `plan`, and the call synchronises `stream` once
+ *      to read the counts back.  b200sp_spmv_launch then runs one kernel per non-empty bin,
+ *      concurrently: lane groups over all rows for the short ones, a warp per medium row, a CTA
+ *      per long row.
  * Returns cudaErrorInvalidValue when plan_bytes is too small. */
-int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols, int64_t nnz,
-                        int val_type, void *plan, size_t plan_bytes, int32_t *long_rows, void *stream);
+int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void *plan, size_t plan_bytes,
+                        int32_t *plan_info, void *stream);
 
 /* y = alpha * A * x + beta * y, A in CSR with int32 zero-based indices.
  * comp_type is B200SP_F32 or B200SP_I32; x has val_type; y has out_type.
- * `plan` / `long_rows` come from b200sp_spmv_analyze for the same row_ptr / col_ind / shape
- * (long_rows = 0 if it was called with long_rows == NULL).
- * With plan == NULL a row-group kernel that needs no workspace is used. */
+ * `plan` / `plan_info` come from b200sp_spmv_analyze for the same row_ptr / rows / nnz (plan_info =
+ * NULL for a tile plan).  With plan == NULL a row-group kernel that needs no workspace is used. */
 int b200sp_spmv_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *x, void *y,
                        int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars, int comp_type,
-                       int val_type, int out_type, void *plan, int32_t long_rows, void *stream);
+                       int val_type, int out_type, void *plan, const int32_t *plan_info, void *stream);
 
 /* y = alpha * A^T * x + beta * y (y has `cols` entries).  First scales y by beta, then
  * scatters alpha * x[i] * a_ij into y[j] with atomic adds.  For 16-bit y an fp32

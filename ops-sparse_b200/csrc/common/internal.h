@@ -57,9 +57,7 @@ struct ActivePlan {
     int64_t nnz = 0;
     int64_t n = 0;         // SpMM only: dense column count the partial-sum area was sized for
     int32_t segments = 0;  // SpMM only: long-row segments found by the analysis
-    const void *colInd = nullptr;  // SpMV only: the column array the long-row cuts were made on
-    int64_t cols = 0;              // SpMV only
-    int32_t longRows = 0;          // SpMV only: rows routed to the long-row kernel
+    int32_t spmvInfo[4] = {0, 0, 0, 0};  // SpMV only: plan_info written by b200sp_spmv_analyze
 };
 
 }  // namespace b200sp

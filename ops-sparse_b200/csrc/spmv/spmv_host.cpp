@@ -153,7 +153,7 @@ b200spScalars ReadScalars(const aclsparseContext *h, const void *alpha, const vo
 bool PlanMatches(const ActivePlan &p, const void *buffer, const aclsparseSpMatDescr *A)
 {
     return buffer != nullptr && p.kind == PlanKind::kSpmv && p.buffer == buffer && p.rowPtr == A->offsets &&
-           p.colInd == A->indices && p.rows == A->rows && p.cols == A->cols && p.nnz == A->nnz;
+           p.rows == A->rows && p.nnz == A->nnz;
 }
 
 }  // namespace
@@ -172,7 +172,7 @@ aclsparseStatus_t aclsparseSpMVGetBufferSize(aclsparseHandle_t handle, aclsparse
     const aclsparseStatus_t st =
         ValidateSpmv("aclsparseSpMVGetBufferSize", handle, opA, matA, vecX, vecY, computeType, alg, &c);
     if (st != ACL_SPARSE_STATUS_SUCCESS) return st;
-    const size_t plan = b200sp_spmv_plan_bytes(matA->rows, matA->cols, matA->nnz, c.valType);
+    const size_t plan = b200sp_spmv_plan_bytes(matA->rows, matA->nnz);
     const size_t trans = TransScratchBytes(c);
     size_t need = c.trans ? trans : plan;
     if (need == 0) need = 256;  // never report 0: callers malloc the result
@@ -193,25 +193,20 @@ aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, aclsparseOpe
     if (st != ACL_SPARSE_STATUS_SUCCESS) return st;
     if (externalBuffer == nullptr) return ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES;
     if (c.trans) return ACL_SPARSE_STATUS_SUCCESS;  // the scatter path has nothing to analyse
-    const size_t bytes = b200sp_spmv_plan_bytes(matA->rows, matA->cols, matA->nnz, c.valType);
-    int32_t longRows = 0;
-    // Preprocess is the one place that may synchronise: it asks for the long-row routing too.
-    const int rc = b200sp_spmv_analyze(static_cast<const int32_t *>(matA->offsets),
-                                       static_cast<const int32_t *>(matA->indices), matA->rows, matA->cols, matA->nnz,
-                                       c.valType, externalBuffer, bytes, &longRows, handle->stream);
+    const size_t bytes = b200sp_spmv_plan_bytes(matA->rows, matA->nnz);
+    ActivePlan p;
+    // Preprocess is the one place that may synchronise: it asks for the binned plan.
+    const int rc = b200sp_spmv_analyze(static_cast<const int32_t *>(matA->offsets), matA->rows, matA->nnz,
+                                       externalBuffer, bytes, p.spmvInfo, handle->stream);
     if (rc != 0) {
         B200SP_LOGE("aclsparseSpMVPreprocess: analysis failed (cuda error %d)", rc);
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
-    ActivePlan p;
     p.buffer = externalBuffer;
     p.kind = PlanKind::kSpmv;
     p.rowPtr = matA->offsets;
-    p.colInd = matA->indices;
     p.rows = matA->rows;
-    p.cols = matA->cols;
     p.nnz = matA->nnz;
-    p.longRows = longRows;
     matA->active = p;
     return ACL_SPARSE_STATUS_SUCCESS;
 }
@@ -246,18 +241,17 @@ aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOperation_t o
                                       scratchBytes, stream);
     } else {
         void *plan = nullptr;
-        int32_t longRows = 0;
+        const int32_t *info = nullptr;
         if (PlanMatches(matA->active, externalBuffer, matA)) {
             plan = externalBuffer;  // analysed by Preprocess: nothing to redo
-            longRows = matA->active.longRows;
+            info = matA->active.spmvInfo;
         } else {
-            // Per-call analysis stays asynchronous: tile table only, every row in the tiles.
-            const size_t bytes = b200sp_spmv_plan_bytes(matA->rows, 0, matA->nnz, c.valType);
+            // Per-call analysis stays asynchronous: a tile plan, in the caller's buffer or the handle workspace.
+            const size_t bytes = b200sp_spmv_tile_plan_bytes(matA->rows, matA->nnz);
             if (externalBuffer != nullptr) plan = externalBuffer;
             else if (handle->WorkspaceBytes() >= bytes) plan = handle->Workspace();
             if (plan != nullptr) {
-                rc = b200sp_spmv_analyze(rowPtr, nullptr, matA->rows, 0, matA->nnz, c.valType, plan, bytes, nullptr,
-                                         stream);
+                rc = b200sp_spmv_analyze(rowPtr, matA->rows, matA->nnz, plan, bytes, nullptr, stream);
                 if (rc != 0) {
                     B200SP_LOGE("aclsparseSpMV: analysis launch failed (cuda error %d)", rc);
                     return ACL_SPARSE_STATUS_EXECUTION_FAILED;
@@ -265,7 +259,7 @@ aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOperation_t o
             }
         }
         rc = b200sp_spmv_launch(rowPtr, colInd, matA->values, vecX->values, vecY->values, matA->rows, matA->cols,
-                                matA->nnz, &sc, c.compType, c.valType, c.outType, plan, longRows, stream);
+                                matA->nnz, &sc, c.compType, c.valType, c.outType, plan, info, stream);
     }
     if (rc != 0) {
         B200SP_LOGE("aclsparseSpMV: kernel launch failed (cuda error %d)", rc);

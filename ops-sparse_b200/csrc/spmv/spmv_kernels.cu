@@ -50,38 +50,18 @@ constexpr int kVecPerThread = (kTileItems + 6 + 4 * kTileThreads - 1) / (4 * kTi
 
 inline size_t AlignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Long rows: rows of at least kLongLen entries are taken out of the tiles and summed by
-// SpmvLongRowKernel, which stages x in shared memory one block of kXBlockBytes at a time.
+// Rows of at least kLongLen entries form the "long" bin of the binned path (see below).
 #ifndef B200SP_SPMV_LONG_LEN
 #define B200SP_SPMV_LONG_LEN 1024
 #endif
-#ifndef B200SP_SPMV_PIECE_LANES
-#define B200SP_SPMV_PIECE_LANES 8  // lanes that share one (long row, x block) piece
-#endif
 constexpr int kLongLen = B200SP_SPMV_LONG_LEN;
-constexpr int kNoLongRows = 0x7fffffff;
-constexpr int kXBlockBytes = 128 * 1024;    // x slice resident in shared memory per CTA
-constexpr int kMaxXBlocks = 64;             // wider matrices keep every row in the tiles
-constexpr int kLongThreads = 1024;
-constexpr int kMaxSkip = kTileItems / kLongLen + 3;  // long-row pieces that can meet one tile
-static_assert(kLongLen >= 256, "long-row threshold too small for the per-tile skip list");
 
-struct LongHeader {  // first 256 bytes of the long-row part of the plan
-    int32_t count;     // rows routed to the long-row kernel
-    int32_t unsorted;  // set when such a row has descending column indices (path is then not used)
-};
-
-struct PlanLayout {
+struct PlanLayout {  // tile plan: what SpmvTileKernel needs
     int64_t ntiles;
-    int64_t capLong;   // 0 when the long-row path cannot be used for this shape
-    int32_t xBlocks;   // column blocks of x
-    int32_t xBlockElems;
-    size_t offTileRow, offCounters, offHead, offTail, offFlags;
-    size_t offLongHeader, offLongRows, offSegStart, offLongCounters, offLongPartials, offSkip, total;
+    size_t offTileRow, offCounters, offHead, offTail, total;
 };
 
-// cols == 0 gives the tile-only layout (no long-row part).
-inline PlanLayout LayoutFor(int64_t rows, int64_t nnz, int64_t cols = 0, int valBytes = 4)
+inline PlanLayout LayoutFor(int64_t rows, int64_t nnz)
 {
     PlanLayout L;
     L.ntiles = (rows + nnz + kTileItems - 1) / kTileItems;
@@ -89,19 +69,8 @@ inline PlanLayout LayoutFor(int64_t rows, int64_t nnz, int64_t cols = 0, int val
     L.offCounters = AlignUp(L.offTileRow + sizeof(int32_t) * (size_t)(L.ntiles + 1), 256);
     L.offHead = AlignUp(L.offCounters + sizeof(int32_t) * (size_t)L.ntiles, 256);
     L.offTail = AlignUp(L.offHead + 4 * (size_t)L.ntiles, 256);
-    L.offFlags = AlignUp(L.offTail + 4 * (size_t)L.ntiles, 256);
-    L.offLongHeader = AlignUp(L.offFlags + sizeof(int32_t) * (size_t)L.ntiles, 256);
-    L.xBlockElems = kXBlockBytes / valBytes;
-    const int64_t xb = cols > 0 ? (cols + L.xBlockElems - 1) / L.xBlockElems : 0;
-    L.xBlocks = (xb >= 1 && xb <= kMaxXBlocks) ? (int32_t)xb : 0;
-    L.capLong = (L.xBlocks > 0 && nnz >= kLongLen) ? nnz / kLongLen : 0;
-    L.offLongRows = L.offLongHeader + 256;
-    L.offSegStart = AlignUp(L.offLongRows + sizeof(int32_t) * (size_t)L.capLong, 256);
-    L.offLongCounters = AlignUp(L.offSegStart + sizeof(int32_t) * (size_t)L.capLong * (L.xBlocks + 1), 256);
-    L.offLongPartials = AlignUp(L.offLongCounters + sizeof(int32_t) * (size_t)L.capLong, 256);
-    L.offSkip = AlignUp(L.offLongPartials + 4 * (size_t)L.capLong * L.xBlocks, 256);
-    // per tile: up to kMaxSkip [lo, hi) ranges of entries that belong to long rows
-    L.total = AlignUp(L.offSkip + (L.capLong > 0 ? sizeof(int32_t) * 2 * kMaxSkip * (size_t)L.ntiles : 0), 256);
+    L.total = AlignUp(L.offTail + 4 * (size_t)L.ntiles, 256);
+    if (L.total == 0) L.total = 256;
     return L;
 }
 
@@ -172,8 +141,7 @@ __device__ __forceinline__ CompT GroupSum(CompT v, int lanes)
 // One thread per tile boundary: binary search of diagonal t*kTileItems on the merge grid of
 // (row end offsets, non-zero indices).  tileRow[t] = number of rows that end before the tile.
 __global__ void SpmvTileSearchKernel(const int32_t *__restrict__ rowPtr, int rows, int nnz, int ntiles,
-                                     int32_t *__restrict__ tileRow, int32_t *__restrict__ counters,
-                                     int32_t *__restrict__ flags)
+                                     int32_t *__restrict__ tileRow, int32_t *__restrict__ counters)
 {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t > ntiles) return;
@@ -188,85 +156,7 @@ __global__ void SpmvTileSearchKernel(const int32_t *__restrict__ rowPtr, int row
         else hi = mid;
     }
     tileRow[t] = (int32_t)lo;
-    if (t < ntiles) {
-        counters[t] = 0;
-        flags[t] = 0;
-    }
-}
-
-// Appends every row of at least kLongLen entries to the long-row list (slot order is arbitrary;
-// no result depends on it).
-__global__ void SpmvFindLongRowsKernel(const int32_t *__restrict__ rowPtr, int rows, LongHeader *hdr,
-                                       int32_t *__restrict__ longRows, int32_t *__restrict__ longCounters)
-{
-    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
-         r += (long long)gridDim.x * blockDim.x) {
-        if (rowPtr[r + 1] - rowPtr[r] >= kLongLen) {
-            const int slot = atomicAdd(&hdr->count, 1);
-            longRows[slot] = (int32_t)r;
-            longCounters[slot] = 0;
-        }
-    }
-}
-
-// One warp per long row: checks that its column indices ascend (the column-block cut below is a
-// binary search) and records, for every tile the row meets, which of the tile's entries are its:
-// flags[t] counts the ranges stored in skip[t][..] (a tile can meet at most kMaxSkip long rows).
-__global__ void SpmvMarkLongRowsKernel(const int32_t *__restrict__ rowPtr, const int32_t *__restrict__ colInd,
-                                       LongHeader *hdr, const int32_t *__restrict__ longRows,
-                                       const int32_t *__restrict__ tileRow, int32_t *__restrict__ flags,
-                                       int32_t *__restrict__ skip, long long totalItems)
-{
-    const int lane = threadIdx.x & 31;
-    const int warpsTotal = gridDim.x * (blockDim.x >> 5);
-    const int n = hdr->count;
-    for (int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); slot < n; slot += warpsTotal) {
-        const int r = longRows[slot];
-        const int s = rowPtr[r], e = rowPtr[r + 1];
-        bool bad = false;
-        for (int p = s + lane; p + 1 < e; p += 32) bad |= colInd[p] > colInd[p + 1];
-        if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(&hdr->unsorted, 1);
-        const int tFirst = (int)(((long long)r + s) / kTileItems);
-        const int tLast = (int)(((long long)r + e) / kTileItems);
-        for (int t = tFirst + lane; t <= tLast; t += 32) {
-            const long long d0 = (long long)t * kTileItems;
-            const long long d1 = d0 + kTileItems < totalItems ? d0 + kTileItems : totalItems;
-            const int j0 = (int)(d0 - tileRow[t]);
-            const int j1 = (int)(d1 - tileRow[t + 1]);
-            const int lo = s > j0 ? s : j0;
-            const int hi = e < j1 ? e : j1;
-            if (hi > lo) {
-                const int k = atomicAdd(&flags[t], 1);
-                if (k < kMaxSkip) {
-                    skip[(long long)t * 2 * kMaxSkip + 2 * k] = lo;
-                    skip[(long long)t * 2 * kMaxSkip + 2 * k + 1] = hi;
-                }
-            }
-        }
-    }
-}
-
-// segStart[slot * (xBlocks + 1) + b] = first entry of the row whose column is >= b * xBlockElems.
-__global__ void SpmvLongSegmentsKernel(const int32_t *__restrict__ rowPtr, const int32_t *__restrict__ colInd,
-                                       const LongHeader *hdr, const int32_t *__restrict__ longRows,
-                                       int32_t *__restrict__ segStart, int xBlocks, int xBlockElems)
-{
-    const long long total = (long long)hdr->count * (xBlocks + 1);
-    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total;
-         w += (long long)gridDim.x * blockDim.x) {
-        const int slot = (int)(w / (xBlocks + 1));
-        const int b = (int)(w - (long long)slot * (xBlocks + 1));
-        const int r = longRows[slot];
-        int lo = rowPtr[r], hi = rowPtr[r + 1];
-        if (b == xBlocks) lo = hi;
-        const long long bound = (long long)b * xBlockElems;
-        while (lo < hi) {
-            const int mid = (lo + hi) >> 1;
-            if (colInd[mid] < bound) lo = mid + 1;
-            else hi = mid;
-        }
-        segStart[w] = lo;
-    }
+    if (t < ntiles) counters[t] = 0;
 }
 
 // ---------------------------------------------------------------- tile kernel
@@ -285,9 +175,6 @@ struct TileArgs {
     int32_t *counters;
     CompT *partHead;
     CompT *partTail;
-    const int32_t *tileFlags;  // how many long rows meet this tile
-    const int32_t *tileSkip;   // [tile][kMaxSkip][2]: entry ranges of those rows inside the tile
-    int longLen;               // rows at least this long belong to SpmvLongRowKernel; kNoLongRows = none
 };
 
 template <typename CompT, typename ValT, typename OutT, bool kVec>
@@ -319,31 +206,6 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
     CompT *sProd = reinterpret_cast<CompT *>(smem + prodOff);
     const int base = j0 & ~3;    // products are stored at sProd[index - base]
 
-    // Entry ranges of this tile that belong to long rows (SpmvLongRowKernel sums those rows); the
-    // analysis stored them per tile, so nothing here waits for the row offsets.
-    int nSkip = 0;
-    int skLo[kMaxSkip], skHi[kMaxSkip];
-    if (a.longLen != kNoLongRows) {
-        nSkip = a.tileFlags[t];
-        nSkip = nSkip < kMaxSkip ? nSkip : kMaxSkip;
-        const int32_t *sk = a.tileSkip + (long long)t * 2 * kMaxSkip;
-#pragma unroll
-        for (int i = 0; i < kMaxSkip; ++i) {
-            skLo[i] = i < nSkip ? sk[2 * i] : 0;
-            skHi[i] = i < nSkip ? sk[2 * i + 1] : 0;
-        }
-    }
-    const bool flagged = nSkip > 0;  // same for the whole CTA
-    // the whole tile lies inside one long row: nothing to do here
-    if (R == 0 && nSkip == 1 && skLo[0] <= j0 && skHi[0] >= j1) return;
-    // true when entries [lo, hi) all belong to long rows
-    auto skipped = [&](int lo, int hi) {
-        bool in = false;
-#pragma unroll
-        for (int i = 0; i < kMaxSkip; ++i) in |= (i < nSkip) && skLo[i] <= lo && hi <= skHi[i];
-        return in;
-    };
-
     // y of the first rows that end here, fetched now so that the epilogue does not wait for it
     const CompT betaEarly = a.sc.Beta();
     CompT yEarly = CompT(0);
@@ -356,16 +218,14 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
         const int nvec = (j1 - base + 3) >> 2;  // <= kVecPerThread * kTileThreads
         int4 c[kVecPerThread];
         Quad<ValT> v[kVecPerThread];
-        bool dead[kVecPerThread];  // quad outside the tile's vectors, or wholly inside a long row
 #pragma unroll
         for (int u = 0; u < kVecPerThread; ++u) {
             const int q = tid + u * kTileThreads;
             const int idx = base + 4 * q;
-            dead[u] = q >= nvec || (flagged && skipped(idx, idx + 4));
             c[u] = make_int4(0, 0, 0, 0);
 #pragma unroll
             for (int e = 0; e < 4; ++e) v[u].v[e] = ValT(0);
-            if (!dead[u]) {
+            if (q < nvec) {
                 if (idx + 4 <= a.nnz) {
                     c[u] = __ldcs(reinterpret_cast<const int4 *>(a.colInd + idx));
                     v[u] = LoadQuad(a.val + idx);
@@ -392,8 +252,7 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     // Entries past the end of the arrays were zero-filled above (column 0, value 0).
-                    // so were quads skipped as part of a long row: no gather for either.
-                    const bool live = idx + e < a.nnz && !dead[u];
+                    const bool live = idx + e < a.nnz;
                     const ValT xv = live ? __ldg(a.x + cc[e]) : ValT(0);
                     p[e] = Widen<CompT>(v[u].v[e]) * Widen<CompT>(xv);
                 }
@@ -402,10 +261,6 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
         }
     } else {
         for (int idx = j0 + tid; idx < j1; idx += kTileThreads) {
-            if (flagged && skipped(idx, idx + 1)) {
-                sProd[idx - base] = CompT(0);
-                continue;
-            }
             const int cidx = a.colInd[idx];
             sProd[idx - base] = Widen<CompT>(a.val[idx]) * Widen<CompT>(__ldg(a.x + cidx));
         }
@@ -502,7 +357,6 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
     };
     const bool headContinues = R > 0 && sRow[0] < j0;  // row i0 began in an earlier tile
     for (int k = tid; k < R; k += kTileThreads) {
-        if (a.longLen != kNoLongRows && sRow[k + 1] - sRow[k] >= a.longLen) continue;  // SpmvLongRowKernel writes it
         if (k == 0 && headContinues) {
             a.partHead[t] = sRowSum[0];
             arrive(i0, t);
@@ -518,174 +372,216 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
     if (tid == kTileThreads - 1) {
         const int tailStart = sRow[R] > j0 ? sRow[R] : j0;
         if (i1 < a.rows && j1 > tailStart) {
-            const int tailEnd = a.rowPtr[i1 + 1];
-            if (a.longLen == kNoLongRows || tailEnd - sRow[R] < a.longLen) {
-                a.partTail[t] = scan;  // key == R here: the run of carries that ends the tile
-                arrive(i1, (int)(((long long)i1 + tailEnd) / kTileItems));
-            }
+            a.partTail[t] = scan;  // key == R here: the run of carries that ends the tile
+            arrive(i1, (int)(((long long)i1 + a.rowPtr[i1 + 1]) / kTileItems));
         }
     }
 }
 
-// ---------------------------------------------------------------- long-row kernel
+// ---------------------------------------------------------------- binned path
 
-template <typename CompT, typename ValT, typename OutT>
-struct LongArgs {
-    const int32_t *colInd;
-    const ValT *val;
-    const ValT *x;
-    OutT *y;
-    int cols;
-    int nnz;
-    Scalars<CompT> sc;
-    const LongHeader *hdr;
-    const int32_t *longRows;
-    const int32_t *segStart;   // [slot][xBlocks + 1]
-    int32_t *counters;         // [group], arrivals of the group's column-block CTAs
-    CompT *partials;           // [slot][xBlocks]
-    int xBlocks;
-    int xBlockElems;
-    int groups;                // CTAs per column block
+// Rows are binned by length by the analysis pass and each bin has its own kernel:
+//   short  (<= kShortMax entries)   SpmvShortRowsKernel : G = 2, 4 or 8 lanes per row, all rows scanned
+//   medium (<  kLongLen entries)    SpmvMediumRowsKernel: one warp per listed row
+//   long   (>= kLongLen entries)    SpmvLongListKernel  : one CTA per listed row, 128-bit loads
+// The three kernels write disjoint rows of y and run concurrently (two side streams).
+#ifndef B200SP_SPMV_SHORT_MAX
+#define B200SP_SPMV_SHORT_MAX 32
+#endif
+constexpr int kShortMax = B200SP_SPMV_SHORT_MAX;
+#ifndef B200SP_SPMV_LONG_UNROLL
+#define B200SP_SPMV_LONG_UNROLL 4
+#endif
+constexpr int kLongUnroll = B200SP_SPMV_LONG_UNROLL;  // quads in flight per thread of the long-row kernel
+
+struct BinHeader {  // first 256 bytes of the binned plan
+    int32_t medium;           // rows in the medium list
+    int32_t longs;            // rows in the long list
+    unsigned long long shortNnz;  // entries in short rows (picks the lane-group width)
+    int32_t shortRows;
 };
 
-// CTA (b, g) keeps block b of x (kXBlockBytes) in shared memory and sums, for every long row of
-// its group, the entries whose column falls in that block -- a contiguous piece of the row,
-// because column indices ascend.  One warp per piece; x comes from shared memory, so the only
-// global traffic is the col_ind / values stream.  Eight lanes share a piece.  The last CTA of a
-// row group to finish adds each row's partial sums in block order and writes y.
-template <typename CompT, typename ValT, typename OutT, bool kVec>
-__global__ void __launch_bounds__(kLongThreads) SpmvLongRowKernel(const LongArgs<CompT, ValT, OutT> a)
+__global__ void SpmvBinRowsKernel(const int32_t *__restrict__ rowPtr, int rows, BinHeader *hdr,
+                                  int4 *__restrict__ listM, int4 *__restrict__ listL)
 {
-    extern __shared__ __align__(16) unsigned char sRaw[];
-    ValT *xs = reinterpret_cast<ValT *>(sRaw);
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const int b = blockIdx.x % a.xBlocks;
-    const int g = blockIdx.x / a.xBlocks;
-    const int nLong = a.hdr->count;
-    const int x0 = b * a.xBlockElems;
-    const int xn = a.cols - x0 < a.xBlockElems ? a.cols - x0 : a.xBlockElems;
-
-    // stage the x block
-    constexpr int kPer16 = 16 / (int)sizeof(ValT);
-    if (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) {
-        const int nv = xn / kPer16;
-        const int4 *src = reinterpret_cast<const int4 *>(a.x + x0);
-        int4 *dst = reinterpret_cast<int4 *>(xs);
-        for (int i = tid; i < nv; i += kLongThreads) dst[i] = __ldg(src + i);
-        for (int i = nv * kPer16 + tid; i < xn; i += kLongThreads) xs[i] = a.x[x0 + i];
-    } else {
-        for (int i = tid; i < xn; i += kLongThreads) xs[i] = a.x[x0 + i];
-    }
-    __syncthreads();
-
-    const ValT *xrel = xs - x0;  // xrel[col] is x[col] for the columns of this block
-    // kPieceLanes lanes share one piece, so a warp has 32 / kPieceLanes pieces in flight.
-    constexpr int kPieceLanes = B200SP_SPMV_PIECE_LANES;
-    constexpr int kUnroll = 4;  // quads in flight per lane
-    constexpr int kPiecesPerCta = kLongThreads / kPieceLanes;
-    const int pl = tid & (kPieceLanes - 1);
-    const int piece = tid / kPieceLanes;
-    const int stride = a.groups * kPiecesPerCta;
-    const int first = g * kPiecesPerCta + piece;
-    const int trips = nLong > g * kPiecesPerCta ? (nLong - g * kPiecesPerCta + stride - 1) / stride : 0;  // CTA-uniform
-    // piece bounds are fetched one trip ahead so that a trip starts with its loads, not a wait
-    auto loadBounds = [&](int slot, int &s, int &e) {
-        s = 0;
-        e = 0;
-        if (slot < nLong) {
-            const int32_t *seg = a.segStart + (long long)slot * (a.xBlocks + 1) + b;
-            s = seg[0];
-            e = seg[1];
-        }
-    };
-    int sCur, eCur, sNext, eNext;
-    loadBounds(first, sCur, eCur);
-    for (int it = 0; it < trips; ++it) {
-        const int slot = first + it * stride;
-        loadBounds(slot + stride, sNext, eNext);
-        const int s = sCur, e = eCur;
-        CompT sum = CompT(0);
-        if (e > s) {
-            if (kVec) {
-                // whole aligned quads [vs, ve) in the middle, up to three single entries at either end;
-                // the single entries are requested first and used last
-                const int vs = (s + 3) >> 2;
-                const int ve = e >> 2;
-                const int headEnd = 4 * vs < e ? 4 * vs : e;
-                const int ph = s + pl;
-                const int pt = 4 * ve + pl;
-                const bool doHead = pl < 4 && ph < headEnd;
-                const bool doTail = pl < 4 && ve >= vs && pt < e;
-                const int ch = doHead ? a.colInd[ph] : x0, ct = doTail ? a.colInd[pt] : x0;
-                const ValT vh = doHead ? a.val[ph] : ValT(0), vt = doTail ? a.val[pt] : ValT(0);
-                for (int v = vs + pl; v < ve; v += kUnroll * kPieceLanes) {
-                    int4 c[kUnroll];
-                    Quad<ValT> q[kUnroll];
-#pragma unroll
-                    for (int u = 0; u < kUnroll; ++u) {
-                        const int vv = v + kPieceLanes * u;
-                        if (vv < ve) {
-                            c[u] = __ldcs(reinterpret_cast<const int4 *>(a.colInd) + vv);
-                            q[u] = LoadQuad(a.val + 4 * vv);
-                        } else {
-                            c[u] = make_int4(x0, x0, x0, x0);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) q[u].v[k] = ValT(0);
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < kUnroll; ++u) {
-                        sum += Widen<CompT>(q[u].v[0]) * Widen<CompT>(xrel[c[u].x]);
-                        sum += Widen<CompT>(q[u].v[1]) * Widen<CompT>(xrel[c[u].y]);
-                        sum += Widen<CompT>(q[u].v[2]) * Widen<CompT>(xrel[c[u].z]);
-                        sum += Widen<CompT>(q[u].v[3]) * Widen<CompT>(xrel[c[u].w]);
-                    }
-                }
-                sum += Widen<CompT>(vh) * Widen<CompT>(xrel[ch]) + Widen<CompT>(vt) * Widen<CompT>(xrel[ct]);
-            } else {
-                for (int p = s + pl; p < e; p += kPieceLanes)
-                    sum += Widen<CompT>(a.val[p]) * Widen<CompT>(xrel[a.colInd[p]]);
+    const int lane = threadIdx.x & 31;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long rowsPadded = ((long long)rows + stride - 1) / stride * stride;
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rowsPadded; r += stride) {
+        int shortLen = 0, isShort = 0;
+        if (r < rows) {
+            const int rs = rowPtr[r], re = rowPtr[r + 1];
+            const int len = re - rs;
+            // a list entry carries the row's bounds, so its kernel starts on col_ind / values at once
+            if (len >= kLongLen) listL[atomicAdd(&hdr->longs, 1)] = make_int4((int)r, rs, re, 0);
+            else if (len > kShortMax) listM[atomicAdd(&hdr->medium, 1)] = make_int4((int)r, rs, re, 0);
+            else {
+                shortLen = len;
+                isShort = 1;
             }
         }
-        sCur = sNext;
-        eCur = eNext;
-        sum = GroupSum(sum, kPieceLanes);
-        if (pl == 0 && slot < nLong) a.partials[(long long)slot * a.xBlocks + b] = sum;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            shortLen += __shfl_xor_sync(0xffffffffu, shortLen, off);
+            isShort += __shfl_xor_sync(0xffffffffu, isShort, off);
+        }
+        if (lane == 0 && isShort) {
+            atomicAdd(&hdr->shortNnz, (unsigned long long)shortLen);
+            atomicAdd(&hdr->shortRows, isShort);
+        }
     }
+}
 
-    // The CTAs (0..xBlocks-1, g) share the rows of group g: the last of them to get here adds
-    // each row's partial sums in block order and writes y.
-    __shared__ int sLast;
-    __threadfence();
+template <typename CompT, typename ValT, typename OutT, int G>
+__global__ void __launch_bounds__(256) SpmvShortRowsKernel(const int32_t *__restrict__ rowPtr,
+                                                            const int32_t *__restrict__ colInd,
+                                                            const ValT *__restrict__ val,
+                                                            const ValT *__restrict__ x, OutT *__restrict__ y,
+                                                            int rows, Scalars<CompT> sc)
+{
+    const int lane = threadIdx.x & (G - 1);
+    const long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    int s = 0, e = 0;
+    if (r < rows) {
+        s = rowPtr[r];
+        e = rowPtr[r + 1];
+    }
+    const bool mine = r < rows && e - s <= kShortMax;  // longer rows belong to the other kernels
+    if (!mine) e = s;
+    const CompT beta = sc.Beta();
+    CompT yOld = CompT(0);
+    if (mine && lane == 0 && beta != CompT(0)) yOld = Widen<CompT>(y[r]);  // requested now, used at the end
+    CompT sum = CompT(0);
+    // up to four entries per lane in flight
+    for (int p = s + lane; p < e; p += 4 * G) {
+        int c[4];
+        ValT v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const bool in = p + u * G < e;
+            c[u] = in ? __ldcs(colInd + p + u * G) : 0;
+            v[u] = in ? __ldcs(val + p + u * G) : ValT(0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const ValT xv = p + u * G < e ? __ldg(x + c[u]) : ValT(0);
+            sum += Widen<CompT>(v[u]) * Widen<CompT>(xv);
+        }
+    }
+    sum = GroupSum(sum, G);
+    if (mine && lane == 0) {
+        CompT z = sc.Alpha() * sum;
+        if (beta != CompT(0)) z += beta * yOld;
+        y[r] = Narrow<OutT>(z);
+    }
+}
+
+template <typename CompT, typename ValT, typename OutT>
+__global__ void __launch_bounds__(256) SpmvMediumRowsKernel(const int32_t *__restrict__ rowPtr,
+                                                             const int32_t *__restrict__ colInd,
+                                                             const ValT *__restrict__ val,
+                                                             const ValT *__restrict__ x, OutT *__restrict__ y,
+                                                             const int4 *__restrict__ list, int count,
+                                                             Scalars<CompT> sc)
+{
+    (void)rowPtr;
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= count) return;  // whole warps leave together
+    const int4 ent = __ldg(list + i);
+    const int r = ent.x, s = ent.y, e = ent.z;
+    const CompT beta = sc.Beta();
+    CompT yOld = CompT(0);
+    if (lane == 0 && beta != CompT(0)) yOld = Widen<CompT>(y[r]);  // requested now, used at the end
+    CompT sum = CompT(0);
+    for (int p = s + lane; p < e; p += 4 * 32) {
+        int c[4];
+        ValT v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const bool in = p + u * 32 < e;
+            c[u] = in ? __ldcs(colInd + p + u * 32) : 0;
+            v[u] = in ? __ldcs(val + p + u * 32) : ValT(0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const ValT xv = p + u * 32 < e ? __ldg(x + c[u]) : ValT(0);
+            sum += Widen<CompT>(v[u]) * Widen<CompT>(xv);
+        }
+    }
+    sum = GroupSum(sum, 32);
+    if (lane == 0) {
+        CompT z = sc.Alpha() * sum;
+        if (beta != CompT(0)) z += beta * yOld;
+        y[r] = Narrow<OutT>(z);
+    }
+}
+
+template <typename CompT, typename ValT, typename OutT, bool kVec>
+__global__ void __launch_bounds__(256) SpmvLongListKernel(const int32_t *__restrict__ rowPtr,
+                                                           const int32_t *__restrict__ colInd,
+                                                           const ValT *__restrict__ val,
+                                                           const ValT *__restrict__ x, OutT *__restrict__ y,
+                                                           const int4 *__restrict__ list, Scalars<CompT> sc)
+{
+    (void)rowPtr;
+    __shared__ CompT sWarp[8];
+    const int tid = threadIdx.x;
+    const int4 ent = __ldg(list + blockIdx.x);
+    const int r = ent.x, s = ent.y, e = ent.z;
+    const CompT beta = sc.Beta();
+    CompT yOld = CompT(0);
+    if (tid == 0 && beta != CompT(0)) yOld = Widen<CompT>(y[r]);  // requested now, used at the end
+    CompT sum = CompT(0);
+    if (kVec) {
+        // whole aligned quads [vs, ve); up to three single entries before and after them
+        const int vs = (s + 3) >> 2, ve = e >> 2;
+        const int headEnd = 4 * vs < e ? 4 * vs : e;
+        const int ph = s + tid, pt = 4 * ve + (tid - 4);
+        const bool doHead = tid < 4 && ph < headEnd;
+        const bool doTail = tid >= 4 && tid < 8 && ve >= vs && pt < e;
+        const int pe = doHead ? ph : pt;
+        const int ce = (doHead || doTail) ? colInd[pe] : 0;
+        const ValT vE = (doHead || doTail) ? val[pe] : ValT(0);
+        for (int v = vs + tid; v < ve; v += kLongUnroll * 256) {
+            int4 c[kLongUnroll];
+            Quad<ValT> q[kLongUnroll];
+#pragma unroll
+            for (int u = 0; u < kLongUnroll; ++u) {
+                const int vv = v + 256 * u;
+                if (vv < ve) {
+                    c[u] = __ldcs(reinterpret_cast<const int4 *>(colInd) + vv);
+                    q[u] = LoadQuad(val + 4 * vv);
+                } else {
+                    c[u] = make_int4(0, 0, 0, 0);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) q[u].v[k] = ValT(0);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kLongUnroll; ++u) {
+                if (v + 256 * u < ve) {
+                    sum += Widen<CompT>(q[u].v[0]) * Widen<CompT>(__ldg(x + c[u].x));
+                    sum += Widen<CompT>(q[u].v[1]) * Widen<CompT>(__ldg(x + c[u].y));
+                    sum += Widen<CompT>(q[u].v[2]) * Widen<CompT>(__ldg(x + c[u].z));
+                    sum += Widen<CompT>(q[u].v[3]) * Widen<CompT>(__ldg(x + c[u].w));
+                }
+            }
+        }
+        if (doHead || doTail) sum += Widen<CompT>(vE) * Widen<CompT>(__ldg(x + ce));
+    } else {
+        for (int p = s + tid; p < e; p += 256) sum += Widen<CompT>(val[p]) * Widen<CompT>(__ldg(x + colInd[p]));
+    }
+    sum = GroupSum(sum, 32);
+    if ((tid & 31) == 0) sWarp[tid >> 5] = sum;
     __syncthreads();
     if (tid == 0) {
-        const int old = atomicAdd(a.counters + g, 1);
-        sLast = (old == a.xBlocks - 1);
-        if (sLast) a.counters[g] = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (!sLast) return;
-    __threadfence();
-    const CompT alpha = a.sc.Alpha();
-    const CompT beta = a.sc.Beta();
-    for (int i = tid; i < trips * kPiecesPerCta; i += kLongThreads) {
-        const int slot = g * kPiecesPerCta + (i % kPiecesPerCta) + (i / kPiecesPerCta) * stride;
-        if (slot >= nLong) continue;
-        CompT total = CompT(0);
-        const CompT *part = a.partials + (long long)slot * a.xBlocks;
-        for (int bb = 0; bb < a.xBlocks; bb += 8) {  // eight loads in flight, added in block order
-            CompT pv[8];
+        CompT tot = CompT(0);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) pv[k] = bb + k < a.xBlocks ? __ldcg(part + bb + k) : CompT(0);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) total += pv[k];
-        }
-        const int r = a.longRows[slot];
-        CompT z = alpha * total;
-        if (beta != CompT(0)) z += beta * Widen<CompT>(a.y[r]);
-        a.y[r] = Narrow<OutT>(z);
+        for (int w = 0; w < 8; ++w) tot += sWarp[w];
+        CompT z = sc.Alpha() * tot;
+        if (beta != CompT(0)) z += beta * yOld;
+        y[r] = Narrow<OutT>(z);
     }
 }
 
@@ -779,30 +675,36 @@ Scalars<int32_t> MakeScalars<int32_t>(const b200spScalars *s)
 
 int GroupWidthFor(int64_t rows, int64_t nnz)
 {
+#ifdef B200SP_SPMV_FORCE_G
+    return B200SP_SPMV_FORCE_G;
+#endif
     const int64_t avg = rows > 0 ? nnz / rows : 0;
     int G = 1;
     while (G < 32 && G < avg) G <<= 1;
     return G;
 }
 
-// A second stream (and the two events that fork it from / join it to the caller's stream) per
-// device, created at first use.  Holds no device memory.
-struct SideLane {
-    cudaStream_t stream = nullptr;
-    cudaEvent_t fork = nullptr, join = nullptr;
+// Two side streams (and the events that fork them from / join them to the caller's stream) per
+// device, created at first use.  They hold no device memory.
+struct SideLanes {
+    cudaStream_t stream[2] = {nullptr, nullptr};
+    cudaEvent_t fork = nullptr;
+    cudaEvent_t join[2] = {nullptr, nullptr};
 };
 
-SideLane *GetSideLane()
+SideLanes *GetSideLanes()
 {
-    static SideLane lanes[64];
+    static SideLanes lanes[64];
     static bool ready[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     if (!ready[dev]) {
-        SideLane &l = lanes[dev];
-        if (cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) != cudaSuccess) {
+        SideLanes &l = lanes[dev];
+        bool ok = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; i < 2 && ok; ++i)
+            ok = cudaStreamCreateWithFlags(&l.stream[i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&l.join[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {
             (void)cudaGetLastError();
             return nullptr;  // fall back to one stream
         }
@@ -811,29 +713,93 @@ SideLane *GetSideLane()
     return &lanes[dev];
 }
 
-template <typename CompT, typename ValT, typename OutT, bool kVec>
-int LaunchLong(const LongArgs<CompT, ValT, OutT> &la, int blocks, cudaStream_t stream)
+// Binned plan in the caller's buffer: header, list of medium rows, list of long rows.
+struct BinLayout {
+    int64_t capM, capL;
+    size_t offHeader, offListM, offListL, total;
+};
+
+inline BinLayout BinLayoutFor(int64_t rows, int64_t nnz)
 {
-    static bool configured = false;  // this instantiation may use kXBlockBytes of dynamic shared memory
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(SpmvLongRowKernel<CompT, ValT, OutT, kVec>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kXBlockBytes);
+    BinLayout L;
+    const int64_t byNnz = nnz / (kShortMax + 1);
+    L.capM = (byNnz < rows ? byNnz : rows) + 1;
+    L.capL = nnz / kLongLen + 1;
+    L.offHeader = 0;
+    L.offListM = 256;
+    L.offListL = AlignUp(L.offListM + sizeof(int4) * (size_t)L.capM, 256);
+    L.total = AlignUp(L.offListL + sizeof(int4) * (size_t)L.capL, 256);
+    return L;
+}
+
+// plan_info layout shared with the host layer (see b200sp_kernels.h)
+enum { kInfoKind = 0, kInfoMedium = 1, kInfoLong = 2, kInfoGroup = 3 };
+enum { kPlanTiles = 0, kPlanBinned = 1 };
+
+template <typename CompT, typename ValT, typename OutT>
+int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, const ValT *x, OutT *y, int64_t rows,
+                 int64_t nnz, const Scalars<CompT> &sc, void *plan, const int32_t *info, cudaStream_t stream)
+{
+    const BinLayout L = BinLayoutFor(rows, nnz);
+    char *p = static_cast<char *>(plan);
+    const int4 *listM = reinterpret_cast<const int4 *>(p + L.offListM);
+    const int4 *listL = reinterpret_cast<const int4 *>(p + L.offListL);
+    const int nM = info[kInfoMedium], nL = info[kInfoLong], G = info[kInfoGroup];
+    const bool vec = (reinterpret_cast<uintptr_t>(colInd) % 16 == 0) &&
+                     (reinterpret_cast<uintptr_t>(val) % (4 * sizeof(ValT)) == 0);
+    // The kernels write disjoint rows of y; the long and medium bins go to side streams forked
+    // from and joined back into the caller's stream, so all three share the SMs.
+    SideLanes *lanes = (nM > 0 || nL > 0) ? GetSideLanes() : nullptr;
+    cudaStream_t sL = stream, sM = stream;
+    if (lanes != nullptr) {
+        cudaError_t e = cudaEventRecord(lanes->fork, stream);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        sL = lanes->stream[0];
+        sM = lanes->stream[1];
     }
-    SpmvLongRowKernel<CompT, ValT, OutT, kVec><<<(unsigned)blocks, kLongThreads, kXBlockBytes, stream>>>(la);
-    b200sp_note_launches(1);
-    return (int)cudaGetLastError();
+    if (nL > 0) {
+        if (lanes != nullptr && cudaStreamWaitEvent(sL, lanes->fork, 0) != cudaSuccess) return (int)cudaGetLastError();
+        if (vec) SpmvLongListKernel<CompT, ValT, OutT, true><<<(unsigned)nL, 256, 0, sL>>>(rowPtr, colInd, val, x, y, listL, sc);
+        else SpmvLongListKernel<CompT, ValT, OutT, false><<<(unsigned)nL, 256, 0, sL>>>(rowPtr, colInd, val, x, y, listL, sc);
+        b200sp_note_launches(1);
+        if (lanes != nullptr) cudaEventRecord(lanes->join[0], sL);
+    }
+    if (nM > 0) {
+        if (lanes != nullptr && cudaStreamWaitEvent(sM, lanes->fork, 0) != cudaSuccess) return (int)cudaGetLastError();
+        SpmvMediumRowsKernel<CompT, ValT, OutT><<<(unsigned)((nM + 7) / 8), 256, 0, sM>>>(rowPtr, colInd, val, x, y, listM,
+                                                                                          nM, sc);
+        b200sp_note_launches(1);
+        if (lanes != nullptr) cudaEventRecord(lanes->join[1], sM);
+    }
+    if (rows > 0) {
+        const unsigned blocks = (unsigned)((rows * G + 255) / 256);
+        switch (G) {
+            case 2: SpmvShortRowsKernel<CompT, ValT, OutT, 2><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+            case 8: SpmvShortRowsKernel<CompT, ValT, OutT, 8><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+            default: SpmvShortRowsKernel<CompT, ValT, OutT, 4><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+        }
+        b200sp_note_launches(1);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (lanes != nullptr) {
+        if (nL > 0) e = cudaStreamWaitEvent(stream, lanes->join[0], 0);
+        if (e == cudaSuccess && nM > 0) e = cudaStreamWaitEvent(stream, lanes->join[1], 0);
+    }
+    return (int)e;
 }
 
 template <typename CompT, typename ValT, typename OutT>
 int LaunchTyped(const int32_t *rowPtr, const int32_t *colInd, const void *val, const void *x, void *y, int64_t rows,
-                int64_t nnz, const b200spScalars *s, void *plan, cudaStream_t stream, int64_t cols = 0,
-                int32_t longRows = 0)
+                int64_t nnz, const b200spScalars *s, void *plan, const int32_t *info, cudaStream_t stream)
 {
     const Scalars<CompT> sc = MakeScalars<CompT>(s);
+    if (plan != nullptr && info != nullptr && info[kInfoKind] == kPlanBinned)
+        return LaunchBinned<CompT, ValT, OutT>(rowPtr, colInd, static_cast<const ValT *>(val),
+                                               static_cast<const ValT *>(x), static_cast<OutT *>(y), rows, nnz, sc,
+                                               plan, info, stream);
     if (plan != nullptr) {
-        const PlanLayout L = LayoutFor(rows, nnz, cols, (int)sizeof(ValT));
+        const PlanLayout L = LayoutFor(rows, nnz);
         if (L.ntiles == 0) return 0;
         char *p = static_cast<char *>(plan);
         TileArgs<CompT, ValT, OutT> a;
@@ -849,62 +815,12 @@ int LaunchTyped(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
         a.counters = reinterpret_cast<int32_t *>(p + L.offCounters);
         a.partHead = reinterpret_cast<CompT *>(p + L.offHead);
         a.partTail = reinterpret_cast<CompT *>(p + L.offTail);
-        a.tileFlags = reinterpret_cast<const int32_t *>(p + L.offFlags);
-        a.tileSkip = reinterpret_cast<const int32_t *>(p + L.offSkip);
-        const bool useLong = longRows > 0 && L.capLong > 0;
-        a.longLen = useLong ? kLongLen : kNoLongRows;
         const bool vec = (reinterpret_cast<uintptr_t>(colInd) % 16 == 0) &&
                          (reinterpret_cast<uintptr_t>(val) % (4 * sizeof(ValT)) == 0);
-        auto launchTiles = [&]() {
-            if (vec) SpmvTileKernel<CompT, ValT, OutT, true><<<(unsigned)L.ntiles, kTileThreads, 0, stream>>>(a);
-            else SpmvTileKernel<CompT, ValT, OutT, false><<<(unsigned)L.ntiles, kTileThreads, 0, stream>>>(a);
-            b200sp_note_launches(1);
-            return (int)cudaGetLastError();
-        };
-        if (!useLong) return launchTiles();
-
-        LongArgs<CompT, ValT, OutT> la;
-        la.colInd = colInd;
-        la.val = static_cast<const ValT *>(val);
-        la.x = static_cast<const ValT *>(x);
-        la.y = static_cast<OutT *>(y);
-        la.cols = (int)cols;
-        la.nnz = (int)nnz;
-        la.sc = sc;
-        la.hdr = reinterpret_cast<const LongHeader *>(p + L.offLongHeader);
-        la.longRows = reinterpret_cast<const int32_t *>(p + L.offLongRows);
-        la.segStart = reinterpret_cast<const int32_t *>(p + L.offSegStart);
-        la.counters = reinterpret_cast<int32_t *>(p + L.offLongCounters);
-        la.partials = reinterpret_cast<CompT *>(p + L.offLongPartials);
-        la.xBlocks = L.xBlocks;
-        la.xBlockElems = L.xBlockElems;
-        const int sms = b200sp_sm_count();
-        int groups = sms / L.xBlocks;  // one wave: every CTA holds 128 KB of shared memory
-        const int maxGroups = (longRows + kLongThreads / B200SP_SPMV_PIECE_LANES - 1) / (kLongThreads / B200SP_SPMV_PIECE_LANES);
-        if (groups > maxGroups) groups = maxGroups;
-        if (groups < 1) groups = 1;
-        la.groups = groups;
-        // The two kernels write disjoint rows of y: the long-row kernel runs on a side stream
-        // forked from and joined back into the caller's stream, so they share the SMs.
-        SideLane *lane = GetSideLane();
-        cudaStream_t longStream = stream;
-        if (lane != nullptr) {
-            cudaError_t e = cudaEventRecord(lane->fork, stream);
-            if (e == cudaSuccess) e = cudaStreamWaitEvent(lane->stream, lane->fork, 0);
-            if (e != cudaSuccess) return (int)e;
-            longStream = lane->stream;
-        }
-        int rc = vec ? LaunchLong<CompT, ValT, OutT, true>(la, groups * L.xBlocks, longStream)
-                     : LaunchLong<CompT, ValT, OutT, false>(la, groups * L.xBlocks, longStream);
-        if (rc != 0) return rc;
-        if (lane != nullptr) {
-            const cudaError_t e = cudaEventRecord(lane->join, lane->stream);
-            if (e != cudaSuccess) return (int)e;
-        }
-        rc = launchTiles();
-        if (rc != 0) return rc;
-        if (lane != nullptr) return (int)cudaStreamWaitEvent(stream, lane->join, 0);
-        return 0;
+        if (vec) SpmvTileKernel<CompT, ValT, OutT, true><<<(unsigned)L.ntiles, kTileThreads, 0, stream>>>(a);
+        else SpmvTileKernel<CompT, ValT, OutT, false><<<(unsigned)L.ntiles, kTileThreads, 0, stream>>>(a);
+        b200sp_note_launches(1);
+        return (int)cudaGetLastError();
     }
     if (rows == 0) return 0;
     const int G = GroupWidthFor(rows, nnz);
@@ -993,79 +909,73 @@ int b200sp_sm_count(void)
     return cached;
 }
 
-namespace {
-int ValueBytes(int valType)
-{
-    switch (valType) {
-        case B200SP_F16: case B200SP_BF16: return 2;
-        case B200SP_I8: return 1;
-        default: return 4;
-    }
-}
-}  // namespace
+size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz) { return LayoutFor(rows, nnz).total; }
 
-size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t cols, int64_t nnz, int val_type)
+size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t nnz)
 {
-    return LayoutFor(rows, nnz, cols, ValueBytes(val_type)).total;
+    const size_t tiles = LayoutFor(rows, nnz).total;
+    const size_t bins = BinLayoutFor(rows, nnz).total;
+    return tiles > bins ? tiles : bins;  // one buffer serves either plan
 }
 
-int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols, int64_t nnz,
-                        int val_type, void *plan, size_t plan_bytes, int32_t *long_rows, void *stream)
+int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void *plan, size_t plan_bytes,
+                        int32_t *plan_info, void *stream)
 {
-    // Without a place to report the long-row count the tile-only layout is used (cols = 0).
-    const PlanLayout L = LayoutFor(rows, nnz, long_rows != nullptr ? cols : 0, ValueBytes(val_type));
-    if (long_rows != nullptr) *long_rows = 0;
-    if (plan == nullptr || plan_bytes < L.total) return (int)cudaErrorInvalidValue;
-    if (L.ntiles == 0) return 0;
+    const size_t need = plan_info == nullptr ? LayoutFor(rows, nnz).total : BinLayoutFor(rows, nnz).total;
+    if (plan == nullptr || plan_bytes < need) return (int)cudaErrorInvalidValue;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     char *p = static_cast<char *>(plan);
-    const unsigned blocks = (unsigned)((L.ntiles + 1 + 255) / 256);
-    SpmvTileSearchKernel<<<blocks, 256, 0, st>>>(row_ptr, (int)rows, (int)nnz, (int)L.ntiles,
-                                                 reinterpret_cast<int32_t *>(p + L.offTileRow),
-                                                 reinterpret_cast<int32_t *>(p + L.offCounters),
-                                                 reinterpret_cast<int32_t *>(p + L.offFlags));
-    b200sp_note_launches(1);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess || long_rows == nullptr || L.capLong == 0 || col_ind == nullptr) return (int)e;
-
-    // Long-row part: list the rows, check their column order, cut them at the x-block borders.
-    auto *hdr = reinterpret_cast<LongHeader *>(p + L.offLongHeader);
-    auto *rowsList = reinterpret_cast<int32_t *>(p + L.offLongRows);
-    e = cudaMemsetAsync(hdr, 0, 256, st);
+    if (plan_info == nullptr) {
+        // Tile plan: nothing to read back, so nothing synchronises.
+        const PlanLayout L = LayoutFor(rows, nnz);
+        if (L.ntiles == 0) return 0;
+        const unsigned blocks = (unsigned)((L.ntiles + 1 + 255) / 256);
+        SpmvTileSearchKernel<<<blocks, 256, 0, st>>>(row_ptr, (int)rows, (int)nnz, (int)L.ntiles,
+                                                     reinterpret_cast<int32_t *>(p + L.offTileRow),
+                                                     reinterpret_cast<int32_t *>(p + L.offCounters));
+        b200sp_note_launches(1);
+        return (int)cudaGetLastError();
+    }
+    // Binned plan: list the medium and the long rows, then read the counts back (one sync).
+    const BinLayout L = BinLayoutFor(rows, nnz);
+    auto *hdr = reinterpret_cast<BinHeader *>(p + L.offHeader);
+    cudaError_t e = cudaMemsetAsync(hdr, 0, 256, st);
     if (e != cudaSuccess) return (int)e;
-    const int sms = b200sp_sm_count();
-    const long long want = (rows + 255) / 256;
-    SpmvFindLongRowsKernel<<<(unsigned)(want < sms * 16LL ? want : sms * 16LL), 256, 0, st>>>(
-        row_ptr, (int)rows, hdr, rowsList, reinterpret_cast<int32_t *>(p + L.offLongCounters));
-    b200sp_note_launches(1);
-    SpmvMarkLongRowsKernel<<<(unsigned)(sms * 4), 256, 0, st>>>(
-        row_ptr, col_ind, hdr, rowsList, reinterpret_cast<const int32_t *>(p + L.offTileRow),
-        reinterpret_cast<int32_t *>(p + L.offFlags), reinterpret_cast<int32_t *>(p + L.offSkip), rows + nnz);
-    b200sp_note_launches(1);
-    SpmvLongSegmentsKernel<<<(unsigned)(sms * 8), 256, 0, st>>>(row_ptr, col_ind, hdr, rowsList,
-                                                                reinterpret_cast<int32_t *>(p + L.offSegStart),
-                                                                L.xBlocks, L.xBlockElems);
-    b200sp_note_launches(1);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
-    LongHeader host{};
+    if (rows > 0) {
+        const long long want = (rows + 255) / 256;
+        const long long cap = (long long)b200sp_sm_count() * 16;
+        SpmvBinRowsKernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
+            row_ptr, (int)rows, hdr, reinterpret_cast<int4 *>(p + L.offListM),
+            reinterpret_cast<int4 *>(p + L.offListL));
+        b200sp_note_launches(1);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    BinHeader host{};
     e = cudaMemcpyAsync(&host, hdr, sizeof(host), cudaMemcpyDeviceToHost, st);
     if (e != cudaSuccess) return (int)e;
     e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return (int)e;
-    *long_rows = host.unsorted ? 0 : host.count;  // unsorted long rows stay in the tiles
+    const double avgShort = host.shortRows > 0 ? (double)host.shortNnz / host.shortRows : 0.0;
+    plan_info[kInfoKind] = kPlanBinned;
+    plan_info[kInfoMedium] = host.medium;
+    plan_info[kInfoLong] = host.longs;
+#ifdef B200SP_SPMV_FORCE_SHORT_G
+    plan_info[kInfoGroup] = B200SP_SPMV_FORCE_SHORT_G;
+#else
+    plan_info[kInfoGroup] = avgShort < 6.0 ? 2 : (avgShort < 24.0 ? 4 : 8);
+#endif
     return 0;
 }
 
 int b200sp_spmv_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *x, void *y,
                        int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars, int comp_type,
-                       int val_type, int out_type, void *plan, int32_t long_rows, void *stream)
+                       int val_type, int out_type, void *plan, const int32_t *plan_info, void *stream)
 {
+    (void)cols;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int rc = DispatchTypes(comp_type, val_type, out_type, [&]<typename C, typename V, typename O>() {
-        // the tile arrays sit at the same offsets whether or not the plan has a long-row part
-        return LaunchTyped<C, V, O>(row_ptr, col_ind, val, x, y, rows, nnz, scalars, plan, st,
-                                    long_rows > 0 ? cols : 0, long_rows);
+        return LaunchTyped<C, V, O>(row_ptr, col_ind, val, x, y, rows, nnz, scalars, plan, plan_info, st);
     });
     return rc < 0 ? (int)cudaErrorInvalidValue : rc;
 }
@@ -1093,7 +1003,7 @@ namespace {
 // b200sp_spmv_analyze would otherwise write into a caller-allocated workspace.  Every GPU that
 // loads the library carries this array until the process exits.
 constexpr int64_t kNoAllocMaxItems = B200SP_NOALLOC_MAX_ITEMS;
-constexpr size_t kNoAllocBytes = 20 * ((size_t)(kNoAllocMaxItems / kTileItems) + 2) + 6 * 256 + 256;
+constexpr size_t kNoAllocBytes = 16 * ((size_t)(kNoAllocMaxItems / kTileItems) + 2) + 4 * 256;
 static __device__ __align__(256) unsigned char gNoAllocScratch[kNoAllocBytes];
 
 constexpr int kMaxDevices = 64;
@@ -1139,11 +1049,11 @@ extern "C" int b200sp_spmv_f32_noalloc(const int32_t *row_ptr, const int32_t *co
     if (L.ntiles == 0) return 0;
     // The analysis rewrites the tile table and zeroes the arrival counters, so nothing a previous
     // call left in the array is read.
-    const int an = b200sp_spmv_analyze(row_ptr, nullptr, rows, 0, nnz, B200SP_F32, scratch, kNoAllocBytes, nullptr, stream);
+    const int an = b200sp_spmv_analyze(row_ptr, rows, nnz, scratch, kNoAllocBytes, nullptr, stream);
     if (an != 0) return an;
     b200spScalars sc{};
     sc.alpha_f = alpha;
     sc.beta_f = beta;
-    return LaunchTyped<float, float, float>(row_ptr, col_ind, val, x, y, rows, nnz, &sc, scratch,
+    return LaunchTyped<float, float, float>(row_ptr, col_ind, val, x, y, rows, nnz, &sc, scratch, nullptr,
                                             static_cast<cudaStream_t>(stream));
 }

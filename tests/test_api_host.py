@@ -178,22 +178,17 @@ def test_spmv_spmm_argument_checks_without_device(pkg):
 
 def test_buffer_size_formulas(pkg):
     L = pkg.lib()
-    L.b200sp_spmv_plan_bytes.restype = c_size_t
-    L.b200sp_spmv_plan_bytes.argtypes = [c_int64, c_int64, c_int64, c_int]
+    for name in ("b200sp_spmv_plan_bytes", "b200sp_spmv_tile_plan_bytes"):
+        getattr(L, name).restype = c_size_t
+        getattr(L, name).argtypes = [c_int64, c_int64]
     L.b200sp_spmm_plan_bytes.restype = c_size_t
     L.b200sp_spmm_plan_bytes.argtypes = [c_int64, c_int64, c_int64]
-    small = L.b200sp_spmv_plan_bytes(0, 0, 0, 0)
-    assert small >= 256
+    assert L.b200sp_spmv_plan_bytes(0, 0) >= 256
     rows, nnz = 1 << 20, 1 << 25
     tiles = (rows + nnz + 3839) // 3840  # 256 threads x 15 merge items per tile
-    tile_only = L.b200sp_spmv_plan_bytes(rows, 0, nnz, 0)
-    # tile table + counters + two partial arrays + flags, 4 bytes each, 256-byte aligned, + header
-    assert 20 * tiles <= tile_only <= 20 * tiles + 8 * 256
-    full = L.b200sp_spmv_plan_bytes(rows, 1 << 20, nnz, 0)
-    # long-row part: one slot per 1024 entries, 32 column blocks of 128 KB of fp32 x
-    slots = nnz // 1024
-    skip = 4 * 2 * 6 * tiles  # per tile: up to six [lo, hi) ranges owned by long rows
-    assert tile_only + 4 * slots * (1 + 33 + 1 + 32) + skip <= full <= tile_only + 4 * slots * 67 + skip + 10 * 256
-    # too wide for the column-block scheme (more than 64 blocks): tile-only again
-    assert L.b200sp_spmv_plan_bytes(rows, 1 << 28, nnz, 0) == tile_only
+    tile_plan = L.b200sp_spmv_tile_plan_bytes(rows, nnz)
+    assert 16 * tiles <= tile_plan <= 16 * tiles + 4096   # tile table + counters + two partial arrays, 4 B each
+    # binned plan: a list entry per row that can be longer than 32 entries, one per possible row of 1024+
+    bins = 256 + 16 * (min(rows, nnz // 33) + 1) + 16 * (nnz // 1024 + 1)  # {row, start, end, -} per entry
+    assert max(tile_plan, bins) <= L.b200sp_spmv_plan_bytes(rows, nnz) <= max(tile_plan, bins) + 1024
     assert L.b200sp_spmm_plan_bytes(1 << 18, 1 << 24, 64) >= 2 * ((1 << 24) // 4096) * 64 * 4
