@@ -326,17 +326,17 @@ def gpu_arm(args, synth, oracle):
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = total_ms / K
 
-    # ---- compute-only steps (no broadcast) and per-launch durations for the roofline
+    # ---- compute-only steps (no broadcast): launch duration for the roofline.  A step is one
+    # launch of the dominant kernel (plus, for the binned SpMV, its two sibling kernels running
+    # beside it on side streams), so the duration is the event-bracketed region divided by the steps.
     KL = min(K, 200)
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(KL + 1)]
     barrier()
-    evs[0].record()
-    for i in range(KL):
+    e0.record()
+    for _ in range(KL):
         op.step(alpha, beta, broadcast=False)
-        evs[i + 1].record()
+    e1.record()
     torch.cuda.synchronize()
-    launch_ms = np.array([evs[i].elapsed_time(evs[i + 1]) for i in range(KL)])
-    launch_ms_mean = max_over_ranks(float(launch_ms.mean()))
+    launch_ms_mean = max_over_ranks(e0.elapsed_time(e1) / KL)
 
     # ---- end to end: host buffers in, host result out, every step
     KE = min(K, 200)
@@ -404,8 +404,9 @@ def gpu_arm(args, synth, oracle):
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
                 "kernel": "SpmmFastKernel" if is_spmm else
-                          ("SpmvTileKernel + SpmvLongRowKernel (concurrent)" if launches > K else "SpmvTileKernel"),
-                "launch_ms_mean": launch_ms_mean, "launch_ms_min": float(launch_ms.min()),
+                          ("SpmvShortRowsKernel + SpmvMediumRowsKernel + SpmvLongListKernel (concurrent bins)"
+                           if launches > K else "SpmvShortRowsKernel"),
+                "launch_ms_mean": launch_ms_mean,
                 "algorithmic_bytes_per_launch": my_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.config),
             },
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,

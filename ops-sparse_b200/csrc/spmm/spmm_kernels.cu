@@ -211,7 +211,7 @@ __device__ __forceinline__ void Accumulate(float v, float b, float &acc, float &
 // group call it together with the same s, e (groups of one warp may differ); `trips` is the
 // warp-uniform number of kLanes-wide chunks to walk (>= this group's own need).
 #ifndef B200SP_SPMM_BATCH
-#define B200SP_SPMM_BATCH 8
+#define B200SP_SPMM_BATCH 4
 #endif
 
 template <typename ValT, bool kKahan, int kLanes>
