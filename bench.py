@@ -190,8 +190,13 @@ class CpuGolden:
 
 
 def cpu_baseline(cfg, oracle, threads: int, budget_s: float = 12.0) -> dict:
+    """At most about `budget_s` seconds of wall time on all host threads: the whole matrix when a pass is
+    short (repeated until about a second has been spent), else its leading rows, 3 passes."""
     g = CpuGolden(cfg, oracle, threads)
-    return g.report(g.rows_for(budget_s / 3), 3)
+    rows = g.rows_for(budget_s / 3)
+    sec, _ = g.run(rows, 1)  # also the warm-up pass
+    reps = int(min(200, max(3, round(1.0 / max(sec, 1e-4)))))
+    return g.report(rows, reps)
 
 
 def reference_arm(args, synth, oracle):
@@ -234,7 +239,18 @@ def dtype_name(cfg) -> str:
 
 # DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum +
 # dram__bytes_write.sum); filled from the summaries committed under profiles/.  None = not captured.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "c2": 309_600_000,  # three bin kernels of one product: 147.0 + 101.2 + 61.2 MB
+    "c3": 353_516_032,
+    "c4": 641_619_968,
+}
+# What the counters show to be the busy resource where it is not DRAM.
+BOUND_NOTES = {
+    "c2": "x gathers from uniformly random columns: one 32-byte L2 sector request each; the L1->L2 request "
+          "port (1 per clock per SM) is 68-71 % busy, DRAM 22-25 %; floor of the formulation about 117 us",
+    "c4": "B (67 MB) is gathered from L2: 4.48 GB through L2->L1 per product, L2 slices 71 % and L1 78 % busy",
+    "c5": "B (1.07 GB) exceeds L2: the row gather is DRAM traffic, about 17.5 GB per product (5 x algorithmic)",
+}
 
 
 def torch_dtype(kind: str):
@@ -407,7 +423,8 @@ def gpu_arm(args, synth, oracle):
                           ("SpmvShortRowsKernel + SpmvMediumRowsKernel + SpmvLongListKernel (concurrent bins)"
                            if launches > K else "SpmvShortRowsKernel"),
                 "launch_ms_mean": launch_ms_mean,
-                "algorithmic_bytes_per_launch": my_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.config),
+                "algorithmic_bytes_per_launch": my_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.config) if world == 1 else None,
+                "note": BOUND_NOTES.get(args.config),
             },
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE},

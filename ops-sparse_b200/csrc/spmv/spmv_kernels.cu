@@ -2,20 +2,34 @@
 //
 // The reference's device code for this operator (sparse/spmv/arch22/kernels/spmv_kernel.h:
 // 27-310 non-transpose, 321-640 transpose) gives every core an equal count of rows and
-// walks them one at a time.  Here the work is cut by *merge path* instead: the rows' end
-// markers and the non-zeros form one merged sequence of rows + nnz items and every CTA takes
-// an equal slice (a tile) of it, whatever the row lengths are.  A tile
+// walks them one at a time.  Two designs replace it here, chosen by what the caller set up.
+//
+// Binned path (a buffer analysed once by aclsparseSpMVPreprocess / b200sp_spmv_analyze with
+// plan_info).  The analysis lists the rows of 33..1023 entries ("medium") and of >= 1024
+// entries ("long") as {row, start, end}; a product is then three kernels over disjoint rows
+// of y, forked onto side streams so that they share the SMs:
+//   SpmvShortRowsKernel<G>  every row gets a group of G = 2, 4 or 8 lanes; rows longer than
+//                           32 entries are skipped.  One coalesced pass over row_ptr / y.
+//   SpmvMediumRowsKernel    one warp per listed row, strided by 32.
+//   SpmvLongListKernel      one CTA per listed row, 128-bit loads of col_ind / values.
+// Many light warps, each with a few independent gathers of x in flight, is what keeps the
+// memory system busy on matrices whose columns are scattered; the kernels hold no shared
+// state, so nothing synchronises inside a product.
+//
+// Tile path (no analysed buffer: the tile table is rebuilt into the handle workspace on every
+// call, no host synchronisation; also the entry point that allocates nothing).  The work is
+// cut by *merge path*: the rows' end markers and the non-zeros form one merged sequence of
+// rows + nnz items and every CTA takes an equal slice (a tile) of it, whatever the row
+// lengths are.  A tile
 //   1. streams its slice of col_ind / values with 128-bit evict-first loads, gathers x
 //      through the read-only path and parks the products in shared memory;
 //   2. lets every thread walk 15 consecutive merge items (add a product, or close a row),
 //      then joins rows that span threads with a segmented scan over the threads' carries;
 //   3. writes y with one coalesced pass (alpha * sum + beta * y).
-// Short rows therefore cost a few instructions each (scalar-row work inside a thread), long
-// rows are summed by as many threads as they have items (vector-row), and a row cut by a
-// tile boundary is finished without a second kernel and without waiting: every tile that
-// holds a piece stores its partial sum, then bumps an arrival counter owned by the tile in
-// which the row ends; whichever tile arrives last adds the pieces in tile order (so the
-// result does not depend on scheduling) and writes y.
+// A row cut by a tile boundary is finished without a second kernel and without waiting:
+// every tile that holds a piece stores its partial sum, then bumps an arrival counter owned
+// by the tile in which the row ends; whichever tile arrives last adds the pieces in tile
+// order (so the result does not depend on scheduling) and writes y.
 //
 // Numerics follow the reference golden SpmvCpu (test/spmv/arch22/spmv_test.cpp:156-173):
 // values and x are widened to the compute type before the multiply, sums are kept in the
@@ -432,15 +446,17 @@ __global__ void SpmvBinRowsKernel(const int32_t *__restrict__ rowPtr, int rows, 
     }
 }
 
+// The three bins as device functions of a block index `bid`.  (One fused grid with a role per
+// block range was measured: no faster than three kernels on forked streams on the power-law
+// matrix, 6-12 % slower on the banded one, so each bin is a kernel of its own.)
 template <typename CompT, typename ValT, typename OutT, int G>
-__global__ void __launch_bounds__(256) SpmvShortRowsKernel(const int32_t *__restrict__ rowPtr,
-                                                            const int32_t *__restrict__ colInd,
-                                                            const ValT *__restrict__ val,
-                                                            const ValT *__restrict__ x, OutT *__restrict__ y,
-                                                            int rows, Scalars<CompT> sc)
+__device__ __forceinline__ void ShortRowsBody(unsigned bid, const int32_t *__restrict__ rowPtr,
+                                              const int32_t *__restrict__ colInd, const ValT *__restrict__ val,
+                                              const ValT *__restrict__ x, OutT *__restrict__ y, int rows,
+                                              const Scalars<CompT> &sc)
 {
     const int lane = threadIdx.x & (G - 1);
-    const long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const long long r = ((long long)bid * 256 + threadIdx.x) / G;
     int s = 0, e = 0;
     if (r < rows) {
         s = rowPtr[r];
@@ -477,16 +493,13 @@ __global__ void __launch_bounds__(256) SpmvShortRowsKernel(const int32_t *__rest
 }
 
 template <typename CompT, typename ValT, typename OutT>
-__global__ void __launch_bounds__(256) SpmvMediumRowsKernel(const int32_t *__restrict__ rowPtr,
-                                                             const int32_t *__restrict__ colInd,
-                                                             const ValT *__restrict__ val,
-                                                             const ValT *__restrict__ x, OutT *__restrict__ y,
-                                                             const int4 *__restrict__ list, int count,
-                                                             Scalars<CompT> sc)
+__device__ __forceinline__ void MediumRowsBody(unsigned bid, const int32_t *__restrict__ colInd,
+                                               const ValT *__restrict__ val, const ValT *__restrict__ x,
+                                               OutT *__restrict__ y, const int4 *__restrict__ list, int count,
+                                               const Scalars<CompT> &sc)
 {
-    (void)rowPtr;
     const int lane = threadIdx.x & 31;
-    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int i = (int)bid * 8 + (threadIdx.x >> 5);
     if (i >= count) return;  // whole warps leave together
     const int4 ent = __ldg(list + i);
     const int r = ent.x, s = ent.y, e = ent.z;
@@ -518,16 +531,13 @@ __global__ void __launch_bounds__(256) SpmvMediumRowsKernel(const int32_t *__res
 }
 
 template <typename CompT, typename ValT, typename OutT, bool kVec>
-__global__ void __launch_bounds__(256) SpmvLongListKernel(const int32_t *__restrict__ rowPtr,
-                                                           const int32_t *__restrict__ colInd,
-                                                           const ValT *__restrict__ val,
-                                                           const ValT *__restrict__ x, OutT *__restrict__ y,
-                                                           const int4 *__restrict__ list, Scalars<CompT> sc)
+__device__ __forceinline__ void LongRowBody(unsigned bid, const int32_t *__restrict__ colInd,
+                                            const ValT *__restrict__ val, const ValT *__restrict__ x,
+                                            OutT *__restrict__ y, const int4 *__restrict__ list,
+                                            const Scalars<CompT> &sc, CompT *sWarp)
 {
-    (void)rowPtr;
-    __shared__ CompT sWarp[8];
     const int tid = threadIdx.x;
-    const int4 ent = __ldg(list + blockIdx.x);
+    const int4 ent = __ldg(list + bid);
     const int r = ent.x, s = ent.y, e = ent.z;
     const CompT beta = sc.Beta();
     CompT yOld = CompT(0);
@@ -583,6 +593,36 @@ __global__ void __launch_bounds__(256) SpmvLongListKernel(const int32_t *__restr
         if (beta != CompT(0)) z += beta * yOld;
         y[r] = Narrow<OutT>(z);
     }
+}
+
+template <typename CompT, typename ValT, typename OutT, int G>
+__global__ void __launch_bounds__(256) SpmvShortRowsKernel(const int32_t *__restrict__ rowPtr,
+                                                            const int32_t *__restrict__ colInd,
+                                                            const ValT *__restrict__ val,
+                                                            const ValT *__restrict__ x, OutT *__restrict__ y,
+                                                            int rows, Scalars<CompT> sc)
+{
+    ShortRowsBody<CompT, ValT, OutT, G>(blockIdx.x, rowPtr, colInd, val, x, y, rows, sc);
+}
+
+template <typename CompT, typename ValT, typename OutT>
+__global__ void __launch_bounds__(256) SpmvMediumRowsKernel(const int32_t *__restrict__ colInd,
+                                                             const ValT *__restrict__ val,
+                                                             const ValT *__restrict__ x, OutT *__restrict__ y,
+                                                             const int4 *__restrict__ list, int count,
+                                                             Scalars<CompT> sc)
+{
+    MediumRowsBody<CompT, ValT, OutT>(blockIdx.x, colInd, val, x, y, list, count, sc);
+}
+
+template <typename CompT, typename ValT, typename OutT, bool kVec>
+__global__ void __launch_bounds__(256) SpmvLongListKernel(const int32_t *__restrict__ colInd,
+                                                           const ValT *__restrict__ val,
+                                                           const ValT *__restrict__ x, OutT *__restrict__ y,
+                                                           const int4 *__restrict__ list, Scalars<CompT> sc)
+{
+    __shared__ CompT sWarp[8];
+    LongRowBody<CompT, ValT, OutT, kVec>(blockIdx.x, colInd, val, x, y, list, sc, sWarp);
 }
 
 // ---------------------------------------------------------------- workspace-free kernel
@@ -685,32 +725,56 @@ int GroupWidthFor(int64_t rows, int64_t nnz)
 }
 
 // Two side streams (and the events that fork them from / join them to the caller's stream) per
-// device, created at first use.  They hold no device memory.
+// host thread and device, created at first use and destroyed with the thread.  They hold no
+// device memory.  Per thread, because an event recorded by one caller must not be waited on
+// by another caller's side stream.
 struct SideLanes {
     cudaStream_t stream[2] = {nullptr, nullptr};
     cudaEvent_t fork = nullptr;
     cudaEvent_t join[2] = {nullptr, nullptr};
+    bool ready = false;
+};
+
+struct SideLaneSet {
+    static constexpr int kMaxDevices = 64;
+    SideLanes lanes[kMaxDevices];
+    ~SideLaneSet()
+    {
+        int prev = 0;
+        const bool havePrev = cudaGetDevice(&prev) == cudaSuccess;
+        for (int d = 0; d < kMaxDevices; ++d) {
+            SideLanes &l = lanes[d];
+            if (!l.ready) continue;
+            if (cudaSetDevice(d) != cudaSuccess) continue;
+            for (int i = 0; i < 2; ++i) {
+                if (l.stream[i] != nullptr) (void)cudaStreamDestroy(l.stream[i]);  // runs what is queued, then frees
+                if (l.join[i] != nullptr) (void)cudaEventDestroy(l.join[i]);
+            }
+            if (l.fork != nullptr) (void)cudaEventDestroy(l.fork);
+        }
+        if (havePrev) (void)cudaSetDevice(prev);
+        (void)cudaGetLastError();
+    }
 };
 
 SideLanes *GetSideLanes()
 {
-    static SideLanes lanes[64];
-    static bool ready[64] = {};
+    static thread_local SideLaneSet set;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!ready[dev]) {
-        SideLanes &l = lanes[dev];
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SideLaneSet::kMaxDevices) return nullptr;
+    SideLanes &l = set.lanes[dev];
+    if (!l.ready) {
         bool ok = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess;
         for (int i = 0; i < 2 && ok; ++i)
             ok = cudaStreamCreateWithFlags(&l.stream[i], cudaStreamNonBlocking) == cudaSuccess &&
                  cudaEventCreateWithFlags(&l.join[i], cudaEventDisableTiming) == cudaSuccess;
         if (!ok) {
             (void)cudaGetLastError();
-            return nullptr;  // fall back to one stream
+            return nullptr;  // the caller then runs the three kernels on its own stream
         }
-        ready[dev] = true;
+        l.ready = true;
     }
-    return &lanes[dev];
+    return &l;
 }
 
 // Binned plan in the caller's buffer: header, list of medium rows, list of long rows.
@@ -759,14 +823,14 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
     }
     if (nL > 0) {
         if (lanes != nullptr && cudaStreamWaitEvent(sL, lanes->fork, 0) != cudaSuccess) return (int)cudaGetLastError();
-        if (vec) SpmvLongListKernel<CompT, ValT, OutT, true><<<(unsigned)nL, 256, 0, sL>>>(rowPtr, colInd, val, x, y, listL, sc);
-        else SpmvLongListKernel<CompT, ValT, OutT, false><<<(unsigned)nL, 256, 0, sL>>>(rowPtr, colInd, val, x, y, listL, sc);
+        if (vec) SpmvLongListKernel<CompT, ValT, OutT, true><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
+        else SpmvLongListKernel<CompT, ValT, OutT, false><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
         b200sp_note_launches(1);
         if (lanes != nullptr) cudaEventRecord(lanes->join[0], sL);
     }
     if (nM > 0) {
         if (lanes != nullptr && cudaStreamWaitEvent(sM, lanes->fork, 0) != cudaSuccess) return (int)cudaGetLastError();
-        SpmvMediumRowsKernel<CompT, ValT, OutT><<<(unsigned)((nM + 7) / 8), 256, 0, sM>>>(rowPtr, colInd, val, x, y, listM,
+        SpmvMediumRowsKernel<CompT, ValT, OutT><<<(unsigned)((nM + 7) / 8), 256, 0, sM>>>(colInd, val, x, y, listM,
                                                                                           nM, sc);
         b200sp_note_launches(1);
         if (lanes != nullptr) cudaEventRecord(lanes->join[1], sM);
