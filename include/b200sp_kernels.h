@@ -47,9 +47,9 @@ typedef struct b200spScalars {
 
 /* ------------------------------------------------------------------ SpMV ------------- */
 
-/* Bytes of workspace the SpMV analysis needs for a rows x * matrix with nnz entries
+/* Bytes of workspace the SpMV analysis needs for a rows x cols matrix with nnz entries
  * (enough for either kind of plan below). */
-size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t nnz);
+size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t cols, int64_t nnz);
 /* Bytes a tile plan alone needs (what a per-call analysis with plan_info == NULL writes). */
 size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz);
 
@@ -57,15 +57,19 @@ size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz);
  *  plan_info == NULL : tile plan.  Splits the merged (row-end, nnz) sequence of the CSR matrix into
  *      equal tiles and writes the tile table plus zeroed arrival counters into `plan`.  Nothing
  *      synchronises.  b200sp_spmv_launch then runs the merge-path tile kernel.
- *  plan_info != NULL : binned plan (4 ints are written to it: kind = 1, medium rows, long rows,
+ *  plan_info != NULL : binned plan (4 ints are written to it: kind = 1 or 2, medium rows, long rows,
  *      lane-group width).  Rows are binned by length -- short (<= 32 entries), medium, long (>= 1024)
  *      -- the medium and long rows are listed in `plan`, and the call synchronises `stream` once
  *      to read the counts back.  b200sp_spmv_launch then runs one kernel per non-empty bin,
- *      concurrently: lane groups over all rows for the short ones, a warp per medium row, a CTA
- *      per long row.
+ *      concurrently: lane groups over all rows for the short ones, a warp per medium row, and for
+ *      the long rows either a CTA per row (kind 1) or, when there are at least 64 of them, their
+ *      column indices ascend and cols <= 2,097,152 (kind 2), CTAs that each keep a 32,768-column
+ *      block of x in shared memory and sum the pieces of all long rows that fall into it.  The
+ *      plan of kind 2 depends on col_ind as well as row_ptr.
+ * col_ind may be NULL (kind 2 is then never chosen; a tile plan does not read it).
  * Returns cudaErrorInvalidValue when plan_bytes is too small. */
-int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void *plan, size_t plan_bytes,
-                        int32_t *plan_info, void *stream);
+int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols, int64_t nnz,
+                        void *plan, size_t plan_bytes, int32_t *plan_info, void *stream);
 
 /* y = alpha * A * x + beta * y, A in CSR with int32 zero-based indices.
  * comp_type is B200SP_F32 or B200SP_I32; x has val_type; y has out_type.

@@ -172,7 +172,7 @@ aclsparseStatus_t aclsparseSpMVGetBufferSize(aclsparseHandle_t handle, aclsparse
     const aclsparseStatus_t st =
         ValidateSpmv("aclsparseSpMVGetBufferSize", handle, opA, matA, vecX, vecY, computeType, alg, &c);
     if (st != ACL_SPARSE_STATUS_SUCCESS) return st;
-    const size_t plan = b200sp_spmv_plan_bytes(matA->rows, matA->nnz);
+    const size_t plan = b200sp_spmv_plan_bytes(matA->rows, matA->cols, matA->nnz);
     const size_t trans = TransScratchBytes(c);
     size_t need = c.trans ? trans : plan;
     if (need == 0) need = 256;  // never report 0: callers malloc the result
@@ -193,11 +193,12 @@ aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, aclsparseOpe
     if (st != ACL_SPARSE_STATUS_SUCCESS) return st;
     if (externalBuffer == nullptr) return ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES;
     if (c.trans) return ACL_SPARSE_STATUS_SUCCESS;  // the scatter path has nothing to analyse
-    const size_t bytes = b200sp_spmv_plan_bytes(matA->rows, matA->nnz);
+    const size_t bytes = b200sp_spmv_plan_bytes(matA->rows, matA->cols, matA->nnz);
     ActivePlan p;
     // Preprocess is the one place that may synchronise: it asks for the binned plan.
-    const int rc = b200sp_spmv_analyze(static_cast<const int32_t *>(matA->offsets), matA->rows, matA->nnz,
-                                       externalBuffer, bytes, p.spmvInfo, handle->stream);
+    const int rc = b200sp_spmv_analyze(static_cast<const int32_t *>(matA->offsets),
+                                       static_cast<const int32_t *>(matA->indices), matA->rows, matA->cols,
+                                       matA->nnz, externalBuffer, bytes, p.spmvInfo, handle->stream);
     if (rc != 0) {
         B200SP_LOGE("aclsparseSpMVPreprocess: analysis failed (cuda error %d)", rc);
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
@@ -251,7 +252,7 @@ aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOperation_t o
             if (externalBuffer != nullptr) plan = externalBuffer;
             else if (handle->WorkspaceBytes() >= bytes) plan = handle->Workspace();
             if (plan != nullptr) {
-                rc = b200sp_spmv_analyze(rowPtr, matA->rows, matA->nnz, plan, bytes, nullptr, stream);
+                rc = b200sp_spmv_analyze(rowPtr, colInd, matA->rows, matA->cols, matA->nnz, plan, bytes, nullptr, stream);
                 if (rc != 0) {
                     B200SP_LOGE("aclsparseSpMV: analysis launch failed (cuda error %d)", rc);
                     return ACL_SPARSE_STATUS_EXECUTION_FAILED;

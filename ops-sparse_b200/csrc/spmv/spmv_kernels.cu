@@ -6,15 +6,22 @@
 //
 // Binned path (a buffer analysed once by aclsparseSpMVPreprocess / b200sp_spmv_analyze with
 // plan_info).  The analysis lists the rows of 33..1023 entries ("medium") and of >= 1024
-// entries ("long") as {row, start, end}; a product is then three kernels over disjoint rows
-// of y, forked onto side streams so that they share the SMs:
-//   SpmvShortRowsKernel<G>  every row gets a group of G = 2, 4 or 8 lanes; rows longer than
-//                           32 entries are skipped.  One coalesced pass over row_ptr / y.
-//   SpmvMediumRowsKernel    one warp per listed row, strided by 32.
-//   SpmvLongListKernel      one CTA per listed row, 128-bit loads of col_ind / values.
-// Many light warps, each with a few independent gathers of x in flight, is what keeps the
-// memory system busy on matrices whose columns are scattered; the kernels hold no shared
-// state, so nothing synchronises inside a product.
+// entries ("long", ordered by descending length) as {row, start, end}; a product is then two
+// launches over disjoint rows of y, the first forked onto a side stream so that they share
+// the SMs:
+//   SpmvLongBlockKernel     (64 or more long rows, ascending columns, at most 2 M columns)
+//                           x is cut into blocks of 32768 columns; a CTA keeps one block in
+//                           shared memory and sums the pieces of all long rows that fall into
+//                           it, so the gathers of more than half of the non-zeros of a
+//                           power-law matrix never leave the SM.  The last CTA to finish a group
+//                           of rows adds their per-block partial sums in block order.
+//   SpmvLongListKernel      (otherwise) one CTA per listed row, 128-bit loads.
+//   SpmvMediumShortKernel   one grid: first a warp per listed medium row, then every row gets
+//                           a group of G = 2, 4 or 8 lanes (rows longer than 32 entries are
+//                           skipped).  SpmvShortRowsKernel alone when no row is medium.
+// Gathers of x from scattered columns cost one L2 sector request each, and an SM issues one
+// request per clock: many light warps, each with a few independent gathers in flight, keep
+// that port busy for the medium and short rows, and the long rows stay off it altogether.
 //
 // Tile path (no analysed buffer: the tile table is rebuilt into the handle workspace on every
 // call, no host synchronisation; also the entry point that allocates nothing).  The work is
@@ -394,11 +401,11 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
 
 // ---------------------------------------------------------------- binned path
 
-// Rows are binned by length by the analysis pass and each bin has its own kernel:
-//   short  (<= kShortMax entries)   SpmvShortRowsKernel : G = 2, 4 or 8 lanes per row, all rows scanned
-//   medium (<  kLongLen entries)    SpmvMediumRowsKernel: one warp per listed row
-//   long   (>= kLongLen entries)    SpmvLongListKernel  : one CTA per listed row, 128-bit loads
-// The three kernels write disjoint rows of y and run concurrently (two side streams).
+// Rows are binned by length by the analysis pass and each bin has its own code:
+//   short  (<= kShortMax entries)   ShortRowsBody : G = 2, 4 or 8 lanes per row, all rows scanned
+//   medium (<  kLongLen entries)    MediumRowsBody: one warp per listed row
+//   long   (>= kLongLen entries)    SpmvLongBlockKernel (x blocks in shared memory) or LongRowBody (a CTA per row)
+// Short and medium rows share one grid; the long rows run beside it on a side stream.
 #ifndef B200SP_SPMV_SHORT_MAX
 #define B200SP_SPMV_SHORT_MAX 32
 #endif
@@ -413,7 +420,31 @@ struct BinHeader {  // first 256 bytes of the binned plan
     int32_t longs;            // rows in the long list
     unsigned long long shortNnz;  // entries in short rows (picks the lane-group width)
     int32_t shortRows;
+    int32_t unsorted;         // set when a long row has descending column indices
 };
+
+// Long rows, second form: x is cut into blocks of kXBlockElems columns and every CTA of
+// SpmvLongBlockKernel keeps one block in shared memory, so the gathers of the long rows never
+// leave the SM (the other bins keep the L1 -> L2 request path to themselves).
+#ifndef B200SP_SPMV_XBLOCK_ELEMS
+#define B200SP_SPMV_XBLOCK_ELEMS 32768
+#endif
+#ifndef B200SP_SPMV_LONG_BLOCK_THREADS
+#define B200SP_SPMV_LONG_BLOCK_THREADS 1024
+#endif
+#ifndef B200SP_SPMV_LONG_BLOCK_UNROLL
+#define B200SP_SPMV_LONG_BLOCK_UNROLL 2
+#endif
+constexpr int kXBlockElems = B200SP_SPMV_XBLOCK_ELEMS;  // 128 KB of fp32 x, 64 KB of 16-bit x
+constexpr int kMaxXBlocks = 64;      // wider matrices use SpmvLongListKernel
+constexpr int kMaxLongGroups = 64;   // CTAs per column block
+constexpr int kLongBlockThreads = B200SP_SPMV_LONG_BLOCK_THREADS;
+#ifndef B200SP_SPMV_PIECE_LANES
+#define B200SP_SPMV_PIECE_LANES 8    // lanes that share one (long row, x block) piece
+#endif
+#ifndef B200SP_SPMV_MIN_LONG_BLOCKED
+#define B200SP_SPMV_MIN_LONG_BLOCKED 64  // fewer long rows than this: not worth staging x
+#endif
 
 __global__ void SpmvBinRowsKernel(const int32_t *__restrict__ rowPtr, int rows, BinHeader *hdr,
                                   int4 *__restrict__ listM, int4 *__restrict__ listL)
@@ -443,6 +474,226 @@ __global__ void SpmvBinRowsKernel(const int32_t *__restrict__ rowPtr, int rows, 
             atomicAdd(&hdr->shortNnz, (unsigned long long)shortLen);
             atomicAdd(&hdr->shortRows, isShort);
         }
+    }
+}
+
+// Orders a list of {row, start, end} entries by descending row length (in classes of an
+// eighth of an octave; the order inside a class is arbitrary and no result depends on it), so
+// that the longest rows start first and the rows that share a warp or a CTA are alike.
+// One CTA: the lists hold thousands of rows, not millions.
+__global__ void __launch_bounds__(1024) SpmvSortByLengthKernel(const int32_t *__restrict__ count,
+                                                                const int4 *__restrict__ in, int4 *__restrict__ out)
+{
+    __shared__ int sHist[256];
+    const int tid = threadIdx.x;
+    const int n = *count;
+    auto lengthClass = [](int4 ent) {
+        const int len = ent.z - ent.y;             // >= 33 for every listed row
+        const int k = 31 - __clz(len);             // floor(log2(len)) >= 5
+        const int key = k * 8 + ((len >> (k - 3)) & 7);
+        return 255 - key;                          // descending
+    };
+    if (tid < 256) sHist[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += 1024) atomicAdd(&sHist[lengthClass(in[i])], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int running = 0;
+        for (int d = 0; d < 256; ++d) {
+            const int c = sHist[d];
+            sHist[d] = running;
+            running += c;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += 1024) {
+        const int4 ent = in[i];
+        out[atomicAdd(&sHist[lengthClass(ent)], 1)] = ent;
+    }
+}
+
+// One warp per listed long row: checks that its column indices ascend, then cuts it at the x
+// block boundaries by binary search: segStart[slot * (xBlocks + 1) + b] = first entry of the row
+// whose column is >= b * kXBlockElems.
+__global__ void SpmvLongSegmentsKernel(const int32_t *__restrict__ colInd, BinHeader *hdr,
+                                       const int4 *__restrict__ listL, int32_t *__restrict__ segStart,
+                                       int xBlocks)
+{
+    const int lane = threadIdx.x & 31;
+    const int warpsTotal = gridDim.x * (blockDim.x >> 5);
+    const int n = hdr->longs;
+    for (int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); slot < n; slot += warpsTotal) {
+        const int4 ent = listL[slot];
+        const int s = ent.y, e = ent.z;
+        bool bad = false;
+        for (int p = s + lane; p + 1 < e; p += 32) bad |= colInd[p] > colInd[p + 1];
+        if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(&hdr->unsorted, 1);
+        for (int b = lane; b <= xBlocks; b += 32) {
+            int lo = s, hi = e;
+            if (b == xBlocks) lo = hi;
+            const long long bound = (long long)b * kXBlockElems;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (colInd[mid] < bound) lo = mid + 1;
+                else hi = mid;
+            }
+            segStart[(long long)slot * (xBlocks + 1) + b] = lo;
+        }
+    }
+}
+
+template <typename CompT, typename ValT, typename OutT>
+struct LongBlockArgs {
+    const int32_t *colInd;
+    const ValT *val;
+    const ValT *x;
+    OutT *y;
+    int cols;
+    Scalars<CompT> sc;
+    const int4 *list;          // {row, start, end, 0} per long row
+    const int32_t *segStart;   // [slot][xBlocks + 1]
+    int32_t *counters;         // [group], arrivals of the group's column-block CTAs
+    CompT *partials;           // [slot][xBlocks]
+    int nLong;
+    int xBlocks;
+    int groups;                // CTAs per column block
+};
+
+// CTA (b, g) keeps block b of x in shared memory and sums, for every long row of its group,
+// the entries whose column falls in that block -- a contiguous piece of the row, because the
+// column indices ascend.  kPieceLanes lanes share a piece; x comes from shared memory, so the
+// only global traffic is the col_ind / values stream.  The last CTA of a row group to finish
+// adds each row's partial sums in block order (no wait, fixed order) and writes y.
+template <typename CompT, typename ValT, typename OutT, bool kVec>
+__global__ void __launch_bounds__(kLongBlockThreads) SpmvLongBlockKernel(const LongBlockArgs<CompT, ValT, OutT> a)
+{
+    extern __shared__ __align__(16) unsigned char sRaw[];
+    ValT *xs = reinterpret_cast<ValT *>(sRaw);
+    const int tid = threadIdx.x;
+    const int b = blockIdx.x % a.xBlocks;
+    const int g = blockIdx.x / a.xBlocks;
+    const int nLong = a.nLong;
+    const int x0 = b * kXBlockElems;
+    const int xn = a.cols - x0 < kXBlockElems ? a.cols - x0 : kXBlockElems;
+
+    // stage the x block
+    constexpr int kPer16 = 16 / (int)sizeof(ValT);
+    if (reinterpret_cast<uintptr_t>(a.x) % 16 == 0) {
+        const int nv = xn / kPer16;
+        const int4 *src = reinterpret_cast<const int4 *>(a.x + x0);  // x0 * sizeof(ValT) is a multiple of 16
+        int4 *dst = reinterpret_cast<int4 *>(xs);
+        for (int i = tid; i < nv; i += kLongBlockThreads) dst[i] = __ldg(src + i);
+        for (int i = nv * kPer16 + tid; i < xn; i += kLongBlockThreads) xs[i] = a.x[x0 + i];
+    } else {
+        for (int i = tid; i < xn; i += kLongBlockThreads) xs[i] = a.x[x0 + i];
+    }
+    __syncthreads();
+
+    const ValT *xrel = xs - x0;  // xrel[col] is x[col] for the columns of this block
+    constexpr int kPieceLanes = B200SP_SPMV_PIECE_LANES;
+    constexpr int kUnroll = B200SP_SPMV_LONG_BLOCK_UNROLL;  // quads in flight per lane
+    constexpr int kPiecesPerCta = kLongBlockThreads / kPieceLanes;
+    const int pl = tid & (kPieceLanes - 1);
+    const int piece = tid / kPieceLanes;
+    const int stride = a.groups * kPiecesPerCta;
+    const int first = g * kPiecesPerCta + piece;
+    const int trips = nLong > g * kPiecesPerCta ? (nLong - g * kPiecesPerCta + stride - 1) / stride : 0;  // CTA-uniform
+    // piece bounds are fetched one trip ahead so that a trip starts with its loads, not a wait
+    auto loadBounds = [&](int slot, int &s, int &e) {
+        s = 0;
+        e = 0;
+        if (slot < nLong) {
+            const int32_t *seg = a.segStart + (long long)slot * (a.xBlocks + 1) + b;
+            s = seg[0];
+            e = seg[1];
+        }
+    };
+    int sCur, eCur, sNext, eNext;
+    loadBounds(first, sCur, eCur);
+    for (int it = 0; it < trips; ++it) {
+        const int slot = first + it * stride;
+        loadBounds(slot + stride, sNext, eNext);
+        const int s = sCur, e = eCur;
+        CompT sum = CompT(0);
+        if (e > s) {
+            if (kVec) {
+                // whole aligned quads [vs, ve) in the middle, up to three single entries at either end;
+                // the single entries are requested first and used last
+                const int vs = (s + 3) >> 2;
+                const int ve = e >> 2;
+                const int headEnd = 4 * vs < e ? 4 * vs : e;
+                const int ph = s + pl;
+                const int pt = 4 * ve + pl;
+                const bool doHead = pl < 4 && ph < headEnd;
+                const bool doTail = pl < 4 && ve >= vs && pt < e;
+                const int ch = doHead ? a.colInd[ph] : x0, ct = doTail ? a.colInd[pt] : x0;
+                const ValT vh = doHead ? a.val[ph] : ValT(0), vt = doTail ? a.val[pt] : ValT(0);
+                for (int v = vs + pl; v < ve; v += kUnroll * kPieceLanes) {
+                    int4 c[kUnroll];
+                    Quad<ValT> q[kUnroll];
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) {
+                        const int vv = v + kPieceLanes * u;
+                        if (vv < ve) {
+                            c[u] = __ldcs(reinterpret_cast<const int4 *>(a.colInd) + vv);
+                            q[u] = LoadQuad(a.val + 4 * vv);
+                        } else {
+                            c[u] = make_int4(x0, x0, x0, x0);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) q[u].v[k] = ValT(0);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) {
+                        sum += Widen<CompT>(q[u].v[0]) * Widen<CompT>(xrel[c[u].x]);
+                        sum += Widen<CompT>(q[u].v[1]) * Widen<CompT>(xrel[c[u].y]);
+                        sum += Widen<CompT>(q[u].v[2]) * Widen<CompT>(xrel[c[u].z]);
+                        sum += Widen<CompT>(q[u].v[3]) * Widen<CompT>(xrel[c[u].w]);
+                    }
+                }
+                sum += Widen<CompT>(vh) * Widen<CompT>(xrel[ch]) + Widen<CompT>(vt) * Widen<CompT>(xrel[ct]);
+            } else {
+                for (int p = s + pl; p < e; p += kPieceLanes)
+                    sum += Widen<CompT>(a.val[p]) * Widen<CompT>(xrel[a.colInd[p]]);
+            }
+        }
+        sCur = sNext;
+        eCur = eNext;
+        sum = GroupSum(sum, kPieceLanes);
+        if (pl == 0 && slot < nLong) a.partials[(long long)slot * a.xBlocks + b] = sum;
+    }
+
+    // The CTAs (0..xBlocks-1, g) share the rows of group g: the last of them to get here adds
+    // each row's partial sums in block order and writes y.
+    __shared__ int sLast;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int old = atomicAdd(a.counters + g, 1);
+        sLast = (old == a.xBlocks - 1);
+        if (sLast) a.counters[g] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!sLast) return;
+    __threadfence();
+    const CompT alpha = a.sc.Alpha();
+    const CompT beta = a.sc.Beta();
+    for (int i = tid; i < trips * kPiecesPerCta; i += kLongBlockThreads) {
+        const int slot = g * kPiecesPerCta + (i % kPiecesPerCta) + (i / kPiecesPerCta) * stride;
+        if (slot >= nLong) continue;
+        CompT total = CompT(0);
+        const CompT *part = a.partials + (long long)slot * a.xBlocks;
+        for (int bb = 0; bb < a.xBlocks; bb += 8) {  // eight loads in flight, added in block order
+            CompT pv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) pv[k] = bb + k < a.xBlocks ? __ldcg(part + bb + k) : CompT(0);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) total += pv[k];
+        }
+        const int r = a.list[slot].x;
+        CompT z = alpha * total;
+        if (beta != CompT(0)) z += beta * Widen<CompT>(a.y[r]);
+        a.y[r] = Narrow<OutT>(z);
     }
 }
 
@@ -605,14 +856,21 @@ __global__ void __launch_bounds__(256) SpmvShortRowsKernel(const int32_t *__rest
     ShortRowsBody<CompT, ValT, OutT, G>(blockIdx.x, rowPtr, colInd, val, x, y, rows, sc);
 }
 
-template <typename CompT, typename ValT, typename OutT>
-__global__ void __launch_bounds__(256) SpmvMediumRowsKernel(const int32_t *__restrict__ colInd,
-                                                             const ValT *__restrict__ val,
-                                                             const ValT *__restrict__ x, OutT *__restrict__ y,
-                                                             const int4 *__restrict__ list, int count,
-                                                             Scalars<CompT> sc)
+// Medium and short rows in one grid: blocks [0, ceil(nM / 8)) take eight listed medium rows
+// each (the longer pieces of work start first), the rest sweep all rows for the short ones.
+// One launch instead of two streams: whether two large grids on different streams really
+// overlap depends on how the driver maps streams to hardware queues, which a library cannot see.
+template <typename CompT, typename ValT, typename OutT, int G>
+__global__ void __launch_bounds__(256) SpmvMediumShortKernel(const int32_t *__restrict__ rowPtr,
+                                                              const int32_t *__restrict__ colInd,
+                                                              const ValT *__restrict__ val,
+                                                              const ValT *__restrict__ x, OutT *__restrict__ y,
+                                                              const int4 *__restrict__ listM, int nM, int rows,
+                                                              Scalars<CompT> sc)
 {
-    MediumRowsBody<CompT, ValT, OutT>(blockIdx.x, colInd, val, x, y, list, count, sc);
+    const unsigned mediumBlocks = ((unsigned)nM + 7u) >> 3;
+    if (blockIdx.x < mediumBlocks) MediumRowsBody<CompT, ValT, OutT>(blockIdx.x, colInd, val, x, y, listM, nM, sc);
+    else ShortRowsBody<CompT, ValT, OutT, G>(blockIdx.x - mediumBlocks, rowPtr, colInd, val, x, y, rows, sc);
 }
 
 template <typename CompT, typename ValT, typename OutT, bool kVec>
@@ -724,14 +982,14 @@ int GroupWidthFor(int64_t rows, int64_t nnz)
     return G;
 }
 
-// Two side streams (and the events that fork them from / join them to the caller's stream) per
-// host thread and device, created at first use and destroyed with the thread.  They hold no
-// device memory.  Per thread, because an event recorded by one caller must not be waited on
-// by another caller's side stream.
+// One side stream (and the events that fork it from / join it to the caller's stream) per host
+// thread and device, created at first use and destroyed with the thread.  It holds no device
+// memory.  Per thread, because an event recorded by one caller must not be waited on by
+// another caller's side stream.
 struct SideLanes {
-    cudaStream_t stream[2] = {nullptr, nullptr};
+    cudaStream_t stream[1] = {nullptr};
     cudaEvent_t fork = nullptr;
-    cudaEvent_t join[2] = {nullptr, nullptr};
+    cudaEvent_t join[1] = {nullptr};
     bool ready = false;
 };
 
@@ -746,10 +1004,8 @@ struct SideLaneSet {
             SideLanes &l = lanes[d];
             if (!l.ready) continue;
             if (cudaSetDevice(d) != cudaSuccess) continue;
-            for (int i = 0; i < 2; ++i) {
-                if (l.stream[i] != nullptr) (void)cudaStreamDestroy(l.stream[i]);  // runs what is queued, then frees
-                if (l.join[i] != nullptr) (void)cudaEventDestroy(l.join[i]);
-            }
+            if (l.stream[0] != nullptr) (void)cudaStreamDestroy(l.stream[0]);  // runs what is queued, then frees
+            if (l.join[0] != nullptr) (void)cudaEventDestroy(l.join[0]);
             if (l.fork != nullptr) (void)cudaEventDestroy(l.fork);
         }
         if (havePrev) (void)cudaSetDevice(prev);
@@ -764,104 +1020,156 @@ SideLanes *GetSideLanes()
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SideLaneSet::kMaxDevices) return nullptr;
     SideLanes &l = set.lanes[dev];
     if (!l.ready) {
-        bool ok = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess;
-        for (int i = 0; i < 2 && ok; ++i)
-            ok = cudaStreamCreateWithFlags(&l.stream[i], cudaStreamNonBlocking) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&l.join[i], cudaEventDisableTiming) == cudaSuccess;
+        const bool ok = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess &&
+                        cudaStreamCreateWithFlags(&l.stream[0], cudaStreamNonBlocking) == cudaSuccess &&
+                        cudaEventCreateWithFlags(&l.join[0], cudaEventDisableTiming) == cudaSuccess;
         if (!ok) {
             (void)cudaGetLastError();
-            return nullptr;  // the caller then runs the three kernels on its own stream
+            return nullptr;  // the caller then runs the kernels on its own stream
         }
         l.ready = true;
     }
     return &l;
 }
 
-// Binned plan in the caller's buffer: header, list of medium rows, list of long rows.
+// Binned plan in the caller's buffer: header, list of medium rows, list of long rows and, when
+// the matrix is narrow enough for the blocked long-row kernel, that kernel's tables.
 struct BinLayout {
     int64_t capM, capL;
-    size_t offHeader, offListM, offListL, total;
+    int32_t xBlocks;  // column blocks of x; 0 = the blocked long-row kernel is not available
+    size_t offHeader, offListM, offListL, offTmpL, offSegStart, offLongCounters, offPartials, total;
 };
 
-inline BinLayout BinLayoutFor(int64_t rows, int64_t nnz)
+inline BinLayout BinLayoutFor(int64_t rows, int64_t cols, int64_t nnz)
 {
     BinLayout L;
     const int64_t byNnz = nnz / (kShortMax + 1);
     L.capM = (byNnz < rows ? byNnz : rows) + 1;
     L.capL = nnz / kLongLen + 1;
+    const int64_t xb = (cols + kXBlockElems - 1) / kXBlockElems;
+    L.xBlocks = (xb >= 1 && xb <= kMaxXBlocks && nnz / kLongLen >= B200SP_SPMV_MIN_LONG_BLOCKED) ? (int32_t)xb : 0;
     L.offHeader = 0;
     L.offListM = 256;
     L.offListL = AlignUp(L.offListM + sizeof(int4) * (size_t)L.capM, 256);
-    L.total = AlignUp(L.offListL + sizeof(int4) * (size_t)L.capL, 256);
+    L.offTmpL = AlignUp(L.offListL + sizeof(int4) * (size_t)L.capL, 256);  // long rows as found, before ordering
+    L.offSegStart = AlignUp(L.offTmpL + sizeof(int4) * (size_t)L.capL, 256);
+    L.offLongCounters = AlignUp(L.offSegStart + sizeof(int32_t) * (size_t)L.capL * (L.xBlocks > 0 ? L.xBlocks + 1 : 0), 256);
+    L.offPartials = AlignUp(L.offLongCounters + sizeof(int32_t) * kMaxLongGroups, 256);
+    L.total = AlignUp(L.offPartials + 4 * (size_t)L.capL * L.xBlocks, 256);
     return L;
 }
 
 // plan_info layout shared with the host layer (see b200sp_kernels.h)
 enum { kInfoKind = 0, kInfoMedium = 1, kInfoLong = 2, kInfoGroup = 3 };
-enum { kPlanTiles = 0, kPlanBinned = 1 };
+enum { kPlanTiles = 0, kPlanBinned = 1, kPlanBinnedBlocked = 2 };  // blocked: long rows go to SpmvLongBlockKernel
+
+template <typename CompT, typename ValT, typename OutT, bool kVec>
+int LaunchLongBlock(const LongBlockArgs<CompT, ValT, OutT> &la, int blocks, cudaStream_t stream)
+{
+    constexpr int kSmem = kXBlockElems * (int)sizeof(ValT);
+    static bool configured[SideLaneSet::kMaxDevices] = {};  // per device: this instantiation may use kSmem bytes
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SideLaneSet::kMaxDevices) return (int)cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(SpmvLongBlockKernel<CompT, ValT, OutT, kVec>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+    SpmvLongBlockKernel<CompT, ValT, OutT, kVec><<<(unsigned)blocks, kLongBlockThreads, kSmem, stream>>>(la);
+    b200sp_note_launches(1);
+    return (int)cudaGetLastError();
+}
 
 template <typename CompT, typename ValT, typename OutT>
 int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, const ValT *x, OutT *y, int64_t rows,
-                 int64_t nnz, const Scalars<CompT> &sc, void *plan, const int32_t *info, cudaStream_t stream)
+                 int64_t cols, int64_t nnz, const Scalars<CompT> &sc, void *plan, const int32_t *info,
+                 cudaStream_t stream)
 {
-    const BinLayout L = BinLayoutFor(rows, nnz);
+    const BinLayout L = BinLayoutFor(rows, cols, nnz);
     char *p = static_cast<char *>(plan);
     const int4 *listM = reinterpret_cast<const int4 *>(p + L.offListM);
     const int4 *listL = reinterpret_cast<const int4 *>(p + L.offListL);
     const int nM = info[kInfoMedium], nL = info[kInfoLong], G = info[kInfoGroup];
     const bool vec = (reinterpret_cast<uintptr_t>(colInd) % 16 == 0) &&
                      (reinterpret_cast<uintptr_t>(val) % (4 * sizeof(ValT)) == 0);
-    // The kernels write disjoint rows of y; the long and medium bins go to side streams forked
-    // from and joined back into the caller's stream, so all three share the SMs.
-    SideLanes *lanes = (nM > 0 || nL > 0) ? GetSideLanes() : nullptr;
-    cudaStream_t sL = stream, sM = stream;
+    // The kernels write disjoint rows of y.  The long rows go first, to a side stream forked from
+    // and joined back into the caller's stream; medium and short rows follow in one grid.
+    SideLanes *lanes = nL > 0 ? GetSideLanes() : nullptr;
+    cudaStream_t sL = stream;
     if (lanes != nullptr) {
         cudaError_t e = cudaEventRecord(lanes->fork, stream);
         if (e != cudaSuccess) return (int)e;
         sL = lanes->stream[0];
-        sM = lanes->stream[1];
     }
     if (nL > 0) {
         if (lanes != nullptr && cudaStreamWaitEvent(sL, lanes->fork, 0) != cudaSuccess) return (int)cudaGetLastError();
-        if (vec) SpmvLongListKernel<CompT, ValT, OutT, true><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
-        else SpmvLongListKernel<CompT, ValT, OutT, false><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
-        b200sp_note_launches(1);
+        if (info[kInfoKind] == kPlanBinnedBlocked && L.xBlocks > 0) {
+            LongBlockArgs<CompT, ValT, OutT> la;
+            la.colInd = colInd;
+            la.val = val;
+            la.x = x;
+            la.y = y;
+            la.cols = (int)cols;
+            la.sc = sc;
+            la.list = listL;
+            la.segStart = reinterpret_cast<const int32_t *>(p + L.offSegStart);
+            la.counters = reinterpret_cast<int32_t *>(p + L.offLongCounters);
+            la.partials = reinterpret_cast<CompT *>(p + L.offPartials);
+            la.nLong = nL;
+            la.xBlocks = L.xBlocks;
+            // one CTA per SM at most (it holds half of the SM's threads and a block of x)
+            constexpr int kPiecesPerCta = kLongBlockThreads / B200SP_SPMV_PIECE_LANES;
+            int groups = b200sp_sm_count() / L.xBlocks;
+            const int useful = (nL + kPiecesPerCta - 1) / kPiecesPerCta;
+            if (groups > useful) groups = useful;
+            if (groups > kMaxLongGroups) groups = kMaxLongGroups;
+            if (groups < 1) groups = 1;
+            la.groups = groups;
+            const int rcL = vec ? LaunchLongBlock<CompT, ValT, OutT, true>(la, L.xBlocks * groups, sL)
+                                : LaunchLongBlock<CompT, ValT, OutT, false>(la, L.xBlocks * groups, sL);
+            if (rcL != 0) return rcL;
+        } else {
+            if (vec) SpmvLongListKernel<CompT, ValT, OutT, true><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
+            else SpmvLongListKernel<CompT, ValT, OutT, false><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
+            b200sp_note_launches(1);
+        }
         if (lanes != nullptr) cudaEventRecord(lanes->join[0], sL);
     }
-    if (nM > 0) {
-        if (lanes != nullptr && cudaStreamWaitEvent(sM, lanes->fork, 0) != cudaSuccess) return (int)cudaGetLastError();
-        SpmvMediumRowsKernel<CompT, ValT, OutT><<<(unsigned)((nM + 7) / 8), 256, 0, sM>>>(colInd, val, x, y, listM,
-                                                                                          nM, sc);
-        b200sp_note_launches(1);
-        if (lanes != nullptr) cudaEventRecord(lanes->join[1], sM);
-    }
     if (rows > 0) {
-        const unsigned blocks = (unsigned)((rows * G + 255) / 256);
-        switch (G) {
-            case 2: SpmvShortRowsKernel<CompT, ValT, OutT, 2><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
-            case 8: SpmvShortRowsKernel<CompT, ValT, OutT, 8><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
-            default: SpmvShortRowsKernel<CompT, ValT, OutT, 4><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+        const unsigned shortBlocks = (unsigned)((rows * G + 255) / 256);
+        if (nM > 0) {
+            const unsigned blocks = (unsigned)((nM + 7) / 8) + shortBlocks;
+            switch (G) {
+                case 2: SpmvMediumShortKernel<CompT, ValT, OutT, 2><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
+                case 8: SpmvMediumShortKernel<CompT, ValT, OutT, 8><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
+                default: SpmvMediumShortKernel<CompT, ValT, OutT, 4><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
+            }
+        } else {
+            switch (G) {
+                case 2: SpmvShortRowsKernel<CompT, ValT, OutT, 2><<<shortBlocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+                case 8: SpmvShortRowsKernel<CompT, ValT, OutT, 8><<<shortBlocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+                default: SpmvShortRowsKernel<CompT, ValT, OutT, 4><<<shortBlocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+            }
         }
         b200sp_note_launches(1);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    if (lanes != nullptr) {
-        if (nL > 0) e = cudaStreamWaitEvent(stream, lanes->join[0], 0);
-        if (e == cudaSuccess && nM > 0) e = cudaStreamWaitEvent(stream, lanes->join[1], 0);
-    }
+    if (lanes != nullptr) e = cudaStreamWaitEvent(stream, lanes->join[0], 0);
     return (int)e;
 }
 
 template <typename CompT, typename ValT, typename OutT>
 int LaunchTyped(const int32_t *rowPtr, const int32_t *colInd, const void *val, const void *x, void *y, int64_t rows,
-                int64_t nnz, const b200spScalars *s, void *plan, const int32_t *info, cudaStream_t stream)
+                int64_t cols, int64_t nnz, const b200spScalars *s, void *plan, const int32_t *info,
+                cudaStream_t stream)
 {
     const Scalars<CompT> sc = MakeScalars<CompT>(s);
-    if (plan != nullptr && info != nullptr && info[kInfoKind] == kPlanBinned)
+    if (plan != nullptr && info != nullptr && info[kInfoKind] != kPlanTiles)
         return LaunchBinned<CompT, ValT, OutT>(rowPtr, colInd, static_cast<const ValT *>(val),
-                                               static_cast<const ValT *>(x), static_cast<OutT *>(y), rows, nnz, sc,
-                                               plan, info, stream);
+                                               static_cast<const ValT *>(x), static_cast<OutT *>(y), rows, cols, nnz,
+                                               sc, plan, info, stream);
     if (plan != nullptr) {
         const PlanLayout L = LayoutFor(rows, nnz);
         if (L.ntiles == 0) return 0;
@@ -975,17 +1283,17 @@ int b200sp_sm_count(void)
 
 size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz) { return LayoutFor(rows, nnz).total; }
 
-size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t nnz)
+size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t cols, int64_t nnz)
 {
     const size_t tiles = LayoutFor(rows, nnz).total;
-    const size_t bins = BinLayoutFor(rows, nnz).total;
+    const size_t bins = BinLayoutFor(rows, cols, nnz).total;
     return tiles > bins ? tiles : bins;  // one buffer serves either plan
 }
 
-int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void *plan, size_t plan_bytes,
-                        int32_t *plan_info, void *stream)
+int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols, int64_t nnz,
+                        void *plan, size_t plan_bytes, int32_t *plan_info, void *stream)
 {
-    const size_t need = plan_info == nullptr ? LayoutFor(rows, nnz).total : BinLayoutFor(rows, nnz).total;
+    const size_t need = plan_info == nullptr ? LayoutFor(rows, nnz).total : BinLayoutFor(rows, cols, nnz).total;
     if (plan == nullptr || plan_bytes < need) return (int)cudaErrorInvalidValue;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     char *p = static_cast<char *>(plan);
@@ -1001,16 +1309,32 @@ int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void 
         return (int)cudaGetLastError();
     }
     // Binned plan: list the medium and the long rows, then read the counts back (one sync).
-    const BinLayout L = BinLayoutFor(rows, nnz);
+    const BinLayout L = BinLayoutFor(rows, cols, nnz);
     auto *hdr = reinterpret_cast<BinHeader *>(p + L.offHeader);
     cudaError_t e = cudaMemsetAsync(hdr, 0, 256, st);
     if (e != cudaSuccess) return (int)e;
+    const bool blocked = L.xBlocks > 0 && col_ind != nullptr;
+    if (blocked) {
+        e = cudaMemsetAsync(p + L.offLongCounters, 0, sizeof(int32_t) * kMaxLongGroups, st);
+        if (e != cudaSuccess) return (int)e;
+    }
     if (rows > 0) {
         const long long want = (rows + 255) / 256;
         const long long cap = (long long)b200sp_sm_count() * 16;
         SpmvBinRowsKernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(
             row_ptr, (int)rows, hdr, reinterpret_cast<int4 *>(p + L.offListM),
-            reinterpret_cast<int4 *>(p + L.offListL));
+            reinterpret_cast<int4 *>(p + L.offTmpL));
+        SpmvSortByLengthKernel<<<1, 1024, 0, st>>>(&hdr->longs, reinterpret_cast<const int4 *>(p + L.offTmpL),
+                                                   reinterpret_cast<int4 *>(p + L.offListL));
+        b200sp_note_launches(2);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (blocked && rows > 0) {
+        // Cut every long row at the x block boundaries (the count of long rows is still on the device).
+        SpmvLongSegmentsKernel<<<(unsigned)(b200sp_sm_count() * 4), 256, 0, st>>>(
+            col_ind, hdr, reinterpret_cast<const int4 *>(p + L.offListL),
+            reinterpret_cast<int32_t *>(p + L.offSegStart), L.xBlocks);
         b200sp_note_launches(1);
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
@@ -1021,7 +1345,8 @@ int b200sp_spmv_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, void 
     e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return (int)e;
     const double avgShort = host.shortRows > 0 ? (double)host.shortNnz / host.shortRows : 0.0;
-    plan_info[kInfoKind] = kPlanBinned;
+    const bool useBlocked = blocked && host.unsorted == 0 && host.longs >= B200SP_SPMV_MIN_LONG_BLOCKED;
+    plan_info[kInfoKind] = useBlocked ? kPlanBinnedBlocked : kPlanBinned;
     plan_info[kInfoMedium] = host.medium;
     plan_info[kInfoLong] = host.longs;
 #ifdef B200SP_SPMV_FORCE_SHORT_G
@@ -1036,10 +1361,9 @@ int b200sp_spmv_launch(const int32_t *row_ptr, const int32_t *col_ind, const voi
                        int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars, int comp_type,
                        int val_type, int out_type, void *plan, const int32_t *plan_info, void *stream)
 {
-    (void)cols;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int rc = DispatchTypes(comp_type, val_type, out_type, [&]<typename C, typename V, typename O>() {
-        return LaunchTyped<C, V, O>(row_ptr, col_ind, val, x, y, rows, nnz, scalars, plan, plan_info, st);
+        return LaunchTyped<C, V, O>(row_ptr, col_ind, val, x, y, rows, cols, nnz, scalars, plan, plan_info, st);
     });
     return rc < 0 ? (int)cudaErrorInvalidValue : rc;
 }
@@ -1097,7 +1421,6 @@ extern "C" int b200sp_spmv_f32_noalloc(const int32_t *row_ptr, const int32_t *co
                                        const float *x, float *y, int64_t rows, int64_t cols, int64_t nnz,
                                        float alpha, float beta, void *stream)
 {
-    (void)cols;
     if (rows < 0 || nnz < 0 || rows > INT32_MAX || nnz > INT32_MAX) return (int)cudaErrorInvalidValue;
     const PlanLayout L = LayoutFor(rows, nnz);
     if (rows + nnz > kNoAllocMaxItems || L.total > kNoAllocBytes) {
@@ -1113,11 +1436,11 @@ extern "C" int b200sp_spmv_f32_noalloc(const int32_t *row_ptr, const int32_t *co
     if (L.ntiles == 0) return 0;
     // The analysis rewrites the tile table and zeroes the arrival counters, so nothing a previous
     // call left in the array is read.
-    const int an = b200sp_spmv_analyze(row_ptr, rows, nnz, scratch, kNoAllocBytes, nullptr, stream);
+    const int an = b200sp_spmv_analyze(row_ptr, nullptr, rows, cols, nnz, scratch, kNoAllocBytes, nullptr, stream);
     if (an != 0) return an;
     b200spScalars sc{};
     sc.alpha_f = alpha;
     sc.beta_f = beta;
-    return LaunchTyped<float, float, float>(row_ptr, col_ind, val, x, y, rows, nnz, &sc, scratch, nullptr,
+    return LaunchTyped<float, float, float>(row_ptr, col_ind, val, x, y, rows, cols, nnz, &sc, scratch, nullptr,
                                             static_cast<cudaStream_t>(stream));
 }

@@ -155,15 +155,44 @@ def test_every_row_length_0_to_130(handle, device, oracle):
         check_against_oracle(oracle, rp, ci, val, x, y, -0.75, 2.0, "f32", "f32", got, what=f"lengths/{mode}")
 
 
+def plan_kind(pkg, device, rp, ci, cols):
+    """kind written by the binned analysis: 1 = a CTA per long row, 2 = long rows summed per column block of x."""
+    from ctypes import c_int32, c_int64, c_size_t, c_void_p
+    L = pkg.lib()
+    L.b200sp_spmv_plan_bytes.restype = c_size_t
+    L.b200sp_spmv_plan_bytes.argtypes = [c_int64, c_int64, c_int64]
+    L.b200sp_spmv_analyze.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p,
+                                      c_void_p]
+    rows, nnz = rp.size - 1, int(rp[-1])
+    d_rp, d_ci = torch.from_numpy(rp).to(device), torch.from_numpy(ci).to(device)
+    nb = L.b200sp_spmv_plan_bytes(rows, cols, nnz)
+    plan = torch.empty(nb, dtype=torch.uint8, device=device)
+    info = (c_int32 * 4)()
+    assert L.b200sp_spmv_analyze(c_void_p(d_rp.data_ptr()), c_void_p(d_ci.data_ptr()), rows, cols, nnz,
+                                 c_void_p(plan.data_ptr()), nb, info, None) == 0
+    torch.cuda.synchronize()
+    return list(info)
+
+
+def many_long_rows(rng, M, N, n_long, lo=1024, hi=6000):
+    lengths = rng.integers(0, 12, size=M)
+    where = rng.choice(M, size=n_long, replace=False)
+    lengths[where] = np.minimum(rng.integers(lo, hi, size=n_long), N)
+    return lengths, where
+
+
 @pytest.mark.parametrize("vt,ot", [("f32", "f32"), ("f16", "f32"), ("bf16", "bf16"), ("i32", "i32")])
-def test_long_rows_take_the_column_blocked_kernel(handle, device, oracle, vt, ot):
-    """Rows of 1024+ entries spread over several 128 KB blocks of x, next to short rows and seams."""
+def test_long_rows_take_the_column_blocked_kernel(handle, device, oracle, pkg, vt, ot):
+    """Many rows of 1024+ entries spread over five blocks of x (the last one partial), next to short rows,
+    rows of exactly 1023 / 1024 entries and very long ones."""
     rng = np.random.default_rng(21)
     M, N = 3000, 150000
-    lengths = rng.integers(0, 12, size=M)
+    lengths, _ = many_long_rows(rng, M, N, 90)
     for r, L in zip((0, 7, 500, 501, 1999, 2999), (1024, 1023, 1500, 5000, 20000, 60000)):
         lengths[r] = L
     rp, ci = random_csr(rng, M, N, lengths)
+    info = plan_kind(pkg, device, rp, ci, N)
+    assert info[0] == 2 and info[2] == int((lengths >= 1024).sum())
     val, x, y = draw(rng, oracle, rp[-1], vt), draw(rng, oracle, N, vt), draw(rng, oracle, M, ot)
     a, b = (2, -1) if ot == "i32" else (1.5, 0.5)
     for mode in ("plan", "workspace"):  # Preprocess routes long rows away; the per-call analysis does not
@@ -171,19 +200,65 @@ def test_long_rows_take_the_column_blocked_kernel(handle, device, oracle, vt, ot
         check_against_oracle(oracle, rp, ci, val, x, y, a, b, vt, ot, got, cols=N, what=f"long rows {vt}/{mode}")
 
 
-def test_unsorted_long_row_stays_in_the_tiles(handle, device, oracle):
-    """The column-block cut needs ascending columns; a long row without them must still be summed right."""
+@pytest.mark.parametrize("N", [20000, 32768, 32769, 65536 + 5])
+def test_column_blocked_kernel_at_block_boundaries(handle, device, oracle, pkg, N):
+    """x of less than one block, exactly one block, one block and one column, two blocks and five columns;
+    dense-ish long rows so that every block boundary is hit, beta = 0."""
+    rng = np.random.default_rng(N)
+    M = 400
+    lengths, _ = many_long_rows(rng, M, N, 70, lo=1024, hi=9000)
+    lengths[3] = N  # a full row: every column, so the first and last column of every block
+    rp, ci = random_csr(rng, M, N, lengths)
+    assert plan_kind(pkg, device, rp, ci, N)[0] == 2
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    got = run_spmv(handle, device, oracle, rp, ci, val, x, y, -2.0, 0.0, "f32", "f32", rows=M, cols=N)
+    check_against_oracle(oracle, rp, ci, val, x, y, -2.0, 0.0, "f32", "f32", got, cols=N, what=f"blocks N={N}")
+
+
+def test_few_long_rows_keep_a_cta_each(handle, device, oracle, pkg):
+    rng = np.random.default_rng(23)
+    M, N = 2000, 100000
+    lengths = rng.integers(0, 40, size=M)
+    lengths[[5, 900, 1500]] = (1024, 4000, 30000)
+    rp, ci = random_csr(rng, M, N, lengths)
+    assert plan_kind(pkg, device, rp, ci, N)[0] == 1
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    got = run_spmv(handle, device, oracle, rp, ci, val, x, y, 1.0, -1.0, "f32", "f32", rows=M, cols=N)
+    check_against_oracle(oracle, rp, ci, val, x, y, 1.0, -1.0, "f32", "f32", got, cols=N, what="few long rows")
+
+
+def test_unsorted_long_row_turns_the_column_blocks_off(handle, device, oracle, pkg):
+    """The column-block cut needs ascending columns; one long row without them and the whole long bin goes
+    back to a CTA per row, and every row must still be summed right."""
     rng = np.random.default_rng(22)
     M, N = 500, 90000
-    lengths = rng.integers(0, 20, size=M)
-    lengths[100], lengths[300] = 6000, 3000
+    lengths, where = many_long_rows(rng, M, N, 80)
     rp, ci = random_csr(rng, M, N, lengths)
-    seg = ci[rp[100]:rp[101]].copy()
+    assert plan_kind(pkg, device, rp, ci, N)[0] == 2
+    r = int(where[17])
+    seg = ci[rp[r]:rp[r + 1]].copy()
     rng.shuffle(seg)
-    ci[rp[100]:rp[101]] = seg
+    ci[rp[r]:rp[r + 1]] = seg
+    assert plan_kind(pkg, device, rp, ci, N)[0] == 1
     val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
     got = run_spmv(handle, device, oracle, rp, ci, val, x, y, 1.0, 1.0, "f32", "f32", rows=M, cols=N)
     check_against_oracle(oracle, rp, ci, val, x, y, 1.0, 1.0, "f32", "f32", got, cols=N, what="unsorted long row")
+
+
+def test_matrix_too_wide_for_column_blocks(handle, device, oracle, pkg):
+    """More than 64 blocks of 32768 columns: the long rows keep a CTA each."""
+    rng = np.random.default_rng(24)
+    M, N = 300, 64 * 32768 + 1
+    lengths, _ = many_long_rows(rng, M, N, 70, lo=1024, hi=3000)
+    rp, ci = random_csr(rng, M, N, lengths)
+    assert plan_kind(pkg, device, rp, ci, N)[0] == 1
+    assert plan_kind(pkg, device, rp, ci, N - 1)[0] == 2
+    val, x, y = draw(rng, oracle, rp[-1], "f32"), draw(rng, oracle, N, "f32"), draw(rng, oracle, M, "f32")
+    for cols in (N, N - 1):
+        ci2 = np.minimum(ci, cols - 1)  # stays ascending (ties are fine)
+        got = run_spmv(handle, device, oracle, rp, ci2, val, x[:cols], y, 0.5, 0.25, "f32", "f32", rows=M, cols=cols)
+        check_against_oracle(oracle, rp, ci2, val, x[:cols], y, 0.5, 0.25, "f32", "f32", got, cols=cols,
+                             what=f"wide matrix cols={cols}")
 
 
 @pytest.mark.parametrize("shape", ["all_empty", "one_row_huge", "many_empty_then_long", "single_entry", "tall_thin"])
