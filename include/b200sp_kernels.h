@@ -149,6 +149,11 @@ int b200sp_spmm_launch(const int32_t *row_ptr, const int32_t *col_ind, const voi
                        const b200spSpmmShape *shape, const b200spScalars *scalars, int val_type, int out_type,
                        void *plan, int32_t segments, void *stream);
 
+/* 1 when a wait on the copy engine ran out of time in the SpMM row-stream kernel since the library was
+ * loaded (the affected rows of C were then not written), 0 when none did, -1 when the flag cannot be
+ * read.  Synchronises the device. */
+int b200sp_spmm_stream_error(void);
+
 /* Number of streaming multiprocessors of the current device (cached after the first call). */
 int b200sp_sm_count(void);
 

@@ -440,6 +440,343 @@ __global__ void __launch_bounds__(kThreads) SpmmFastKernel(const FastArgs<ValT, 
     }
 }
 
+// ---------------------------------------------------------------- row-stream path
+
+// For B rows of 512 or 1024 bytes.  A warp owns 32 consecutive rows of A and walks their
+// non-zeros as one stream, in CSR order, across the row boundaries; the B row of every entry
+// is brought into shared memory by the copy engine (cp.async.bulk, one row per copy, completion
+// counted on an mbarrier) several batches ahead of its use, so the chain row_ptr -> col_ind ->
+// B row -> C row that bounds a row-at-a-time kernel on matrices full of one- and two-entry
+// rows is paid once per warp, not once per row, and no registers hold data in flight.
+// Every lane owns kRowBytes / 32 bytes of the row; each output keeps one fp32 accumulator
+// that takes its products in CSR order with separate multiply and add, as in the kernel above,
+// so the results are the same bits.  Rows above kLongRow entries are left to the segment CTAs
+// of SpmmFastKernel.
+// Measured on the 2 M x 2 M graph matrix with 512-byte rows (ms per product, segment CTAs included):
+// 3 buffers x 16 rows x 4 warps per CTA 5.28; 2 x 16 x 4 3.97; 2 x 8 x 4 3.29; 2 x 4 x 4 3.38;
+// 2 x 8 x 2 2.99; 2 x 8 x 1 2.91.  Less shared memory per warp means more warps per SM, and
+// one warp per CTA gives the memory of a finished warp back at once.
+#ifndef B200SP_SPMM_STREAM_BUFFERS
+#define B200SP_SPMM_STREAM_BUFFERS 2
+#endif
+#ifndef B200SP_SPMM_STREAM_BATCH_BYTES
+#define B200SP_SPMM_STREAM_BATCH_BYTES 4096
+#endif
+#ifndef B200SP_SPMM_STREAM_WARPS
+#define B200SP_SPMM_STREAM_WARPS 1
+#endif
+constexpr int kStreamBuffers = B200SP_SPMM_STREAM_BUFFERS;  // batches of B rows per warp: one in use, the rest in flight
+constexpr int kStreamWarps = B200SP_SPMM_STREAM_WARPS;
+constexpr int kStreamThreads = kStreamWarps * 32;
+constexpr int kStreamRows = 32;                              // rows of A per warp
+constexpr long long kStreamWaitCycles = 1ll << 31;           // SM clocks (about a second) to wait on one barrier before giving up
+
+__device__ int gStreamError;  // set when a wait ran out (never observed; the kernel then stops writing C)
+
+__device__ __forceinline__ uint32_t SmemAddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void MbarInit(uint64_t *bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void MbarExpectTx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(SmemAddr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Polls with a time limit; false when the limit was reached.
+__device__ __forceinline__ bool MbarWait(uint64_t *bar, uint32_t parity)
+{
+    if (MbarTryWait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!MbarTryWait(bar, parity)) {
+        if (clock64() - t0 > kStreamWaitCycles) return false;
+    }
+    return true;
+}
+// One row: global -> shared through the copy engine; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void BulkLoadRow(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     SmemAddr(dst)),
+                 "l"(src), "r"(bytes), "r"(SmemAddr(bar))
+                 : "memory");
+}
+
+template <int kBytes> struct LaneWords {  // kBytes of shared memory as 32-bit words
+    static constexpr int kWords = kBytes / 4;
+    static __device__ __forceinline__ void Load(const unsigned char *p, uint32_t (&w)[kWords])
+    {
+        if constexpr (kBytes == 4) {
+            w[0] = *reinterpret_cast<const uint32_t *>(p);
+        } else if constexpr (kBytes == 8) {
+            const uint2 q = *reinterpret_cast<const uint2 *>(p);
+            w[0] = q.x; w[1] = q.y;
+        } else {
+            static_assert(kBytes % 16 == 0, "a lane owns 4, 8 or a multiple of 16 bytes of a B row");
+#pragma unroll
+            for (int i = 0; i < kBytes / 16; ++i) {
+                const uint4 q = reinterpret_cast<const uint4 *>(p)[i];
+                w[4 * i] = q.x; w[4 * i + 1] = q.y; w[4 * i + 2] = q.z; w[4 * i + 3] = q.w;
+            }
+        }
+    }
+};
+
+template <typename ValT, int kWords> struct WordsToF32;
+template <int kWords> struct WordsToF32<float, kWords> {
+    static constexpr int kElems = kWords;
+    static __device__ __forceinline__ void Convert(const uint32_t (&w)[kWords], float (&out)[kElems])
+    {
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) out[i] = __uint_as_float(w[i]);
+    }
+};
+template <int kWords> struct WordsToF32<__half, kWords> {
+    static constexpr int kElems = 2 * kWords;
+    static __device__ __forceinline__ void Convert(const uint32_t (&w)[kWords], float (&out)[kElems])
+    {
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            out[2 * i] = f.x;
+            out[2 * i + 1] = f.y;
+        }
+    }
+};
+template <int kWords> struct WordsToF32<__nv_bfloat16, kWords> {
+    static constexpr int kElems = 2 * kWords;
+    static __device__ __forceinline__ void Convert(const uint32_t (&w)[kWords], float (&out)[kElems])
+    {
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) {  // bf16 -> fp32 is a 16-bit shift
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+// E consecutive outputs of one lane: z = alpha * acc + beta * old, stored with the widest aligned vector.
+template <typename OutT, int E>
+__device__ __forceinline__ void LoadOld(const OutT *src, float (&old)[E])
+{
+#pragma unroll
+    for (int i = 0; i < E; ++i) old[i] = ToF32(src[i]);  // contiguous: the compiler merges these into vector loads
+}
+template <typename OutT, int E>
+__device__ __forceinline__ void StoreSlice(OutT *dst, const float (&acc)[E], const float (&old)[E], float alpha,
+                                           float beta)
+{
+    float z[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i)
+        z[i] = beta != 0.0f ? __fadd_rn(__fmul_rn(alpha, acc[i]), __fmul_rn(beta, old[i])) : __fmul_rn(alpha, acc[i]);
+    constexpr int kBytes = E * (int)sizeof(OutT);
+    alignas(16) OutT o[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) o[i] = FromF32<OutT>(z[i]);
+    if constexpr (kBytes % 16 == 0) {
+#pragma unroll
+        for (int i = 0; i < kBytes / 16; ++i)
+            reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(o)[i];
+    } else if constexpr (kBytes == 8) {
+        *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(o);
+    } else {
+        static_assert(kBytes == 4, "a lane writes 4, 8 or a multiple of 16 bytes of a C row");
+        *reinterpret_cast<uint32_t *>(dst) = *reinterpret_cast<const uint32_t *>(o);
+    }
+}
+
+template <typename ValT, typename OutT>
+struct StreamArgs {
+    const int32_t *rowPtr;
+    const int32_t *colInd;
+    const ValT *val;
+    const ValT *B;
+    OutT *C;
+    int m;
+    long long ldb;
+    long long ldc;
+    ScalarsF sc;
+};
+
+template <int kRowBytes> struct StreamShape {
+    static constexpr int kBatch = B200SP_SPMM_STREAM_BATCH_BYTES / kRowBytes;  // B rows per batch
+    static_assert(kBatch >= 1 && kBatch <= 32, "a lane issues at most one row copy per batch");
+    static constexpr int kWarpBytes = kStreamBuffers * (kBatch * kRowBytes + kBatch * 8) + 64;  // data, val, meta, barriers
+    static constexpr int kCtaBytes = kStreamWarps * kWarpBytes;
+};
+
+template <typename ValT, typename OutT, int kRowBytes>
+__global__ void __launch_bounds__(kStreamThreads) SpmmRowStreamKernel(const StreamArgs<ValT, OutT> a)
+{
+    using Shape = StreamShape<kRowBytes>;
+    constexpr int kBatch = Shape::kBatch;
+    constexpr int kLaneBytes = kRowBytes / 32;
+    constexpr int kWords = kLaneBytes / 4;
+    constexpr int E = WordsToF32<ValT, kWords>::kElems;
+    extern __shared__ __align__(128) unsigned char sRaw[];
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    unsigned char *base = sRaw + (size_t)warp * Shape::kWarpBytes;
+    unsigned char *sData = base;                                                          // [buffers][kBatch][kRowBytes]
+    float *sVal = reinterpret_cast<float *>(base + kStreamBuffers * kBatch * kRowBytes);  // [buffers][kBatch]
+    int *sMeta = reinterpret_cast<int *>(sVal + kStreamBuffers * kBatch);                 // [buffers][kBatch]
+    uint64_t *sBar = reinterpret_cast<uint64_t *>(sMeta + kStreamBuffers * kBatch);       // [buffers]
+
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < kStreamBuffers; ++i) MbarInit(sBar + i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    const float alpha = a.sc.Alpha();
+    const float beta = a.sc.Beta();
+    const long long r0 = ((long long)blockIdx.x * kStreamWarps + warp) * kStreamRows;
+    if (r0 >= a.m) return;
+
+    // This lane's row: bounds, length, and where its entries start in the warp's stream.
+    const long long myRow = r0 + lane;
+    int s = 0, len = 0;
+    bool mine = false;
+    if (myRow < a.m) {
+        s = a.rowPtr[myRow];
+        len = a.rowPtr[myRow + 1] - s;
+        mine = len <= kLongRow;  // longer rows are written by the segment CTAs
+        if (!mine) len = 0;
+    }
+    int off = len;  // inclusive scan over the lanes, then made exclusive
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, off, d);
+        if (lane >= d) off += t;
+    }
+    const int total = __shfl_sync(0xffffffffu, off, 31);
+    off -= len;
+
+    OutT *cRow0 = a.C + r0 * a.ldc + lane * E;
+    // Rows without entries: C = beta * C.
+    unsigned emptyMask = __ballot_sync(0xffffffffu, mine && len == 0);
+    while (emptyMask != 0) {
+        const int l = __ffs(emptyMask) - 1;
+        emptyMask &= emptyMask - 1;
+        float zero[E], old[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) zero[i] = old[i] = 0.0f;
+        OutT *dst = cRow0 + (long long)l * a.ldc;
+        if (beta != 0.0f) LoadOld<OutT, E>(dst, old);
+        StoreSlice<OutT, E>(dst, zero, old, alpha, beta);
+    }
+    if (total == 0) return;
+    const unsigned liveMask = __ballot_sync(0xffffffffu, len > 0);
+
+    const int nBatches = (total + kBatch - 1) / kBatch;
+    // Entry q of the stream (held by lane q % kBatch of its batch): column, value, and which row it
+    // belongs to / whether it ends that row.
+    int eCol = 0, eMeta = 0;
+    float eVal = 0.0f;
+    auto fetchEntries = [&](int k) {
+        const int q = k * kBatch + lane;
+        // last lane whose stream offset is <= q: the row that holds entry q
+        int lo = 0;
+#pragma unroll
+        for (int step = 16; step > 0; step >>= 1) {
+            const int cand = lo + step;
+            const int offC = __shfl_sync(0xffffffffu, off, cand & 31);
+            if (cand < 32 && offC <= q) lo = cand;
+        }
+        const int sL = __shfl_sync(0xffffffffu, s, lo);
+        const int offL = __shfl_sync(0xffffffffu, off, lo);
+        const int lenL = __shfl_sync(0xffffffffu, len, lo);
+        if (lane < kBatch && q < total) {
+            const int p = sL + (q - offL);
+            eCol = __ldcs(a.colInd + p);
+            eVal = ToF32(__ldcs(a.val + p));
+            eMeta = lo | ((q - offL == lenL - 1) ? 0x100 : 0);
+        }
+    };
+    auto issueBatch = [&](int k) {
+        const int buf = k % kStreamBuffers;
+        const int live = total - k * kBatch < kBatch ? total - k * kBatch : kBatch;
+        if (lane == 0) MbarExpectTx(sBar + buf, (uint32_t)live * kRowBytes);
+        __syncwarp();
+        if (lane < live) {
+            sVal[buf * kBatch + lane] = eVal;
+            sMeta[buf * kBatch + lane] = eMeta;
+            BulkLoadRow(sData + ((size_t)buf * kBatch + lane) * kRowBytes, a.B + (long long)eCol * a.ldb, kRowBytes,
+                        sBar + buf);
+        }
+    };
+
+    // prologue: all but one buffer in flight
+    const int ahead = kStreamBuffers - 1;
+    for (int k = 0; k < ahead && k < nBatches; ++k) {
+        fetchEntries(k);
+        issueBatch(k);
+    }
+    if (ahead < nBatches) fetchEntries(ahead);
+
+    float acc[E], old[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) acc[i] = old[i] = 0.0f;
+    // C of the row being summed is requested when the row before it is written (when the warp starts, for the first)
+    if (beta != 0.0f) LoadOld<OutT, E>(cRow0 + (long long)(__ffs(liveMask) - 1) * a.ldc, old);
+
+    int failedAt = -1;
+    for (int k = 0; k < nBatches; ++k) {
+        if (k + ahead < nBatches) issueBatch(k + ahead);           // uses the entries fetched one trip ago
+        if (k + ahead + 1 < nBatches) fetchEntries(k + ahead + 1);  // lands while this batch is summed
+        const int buf = k % kStreamBuffers;
+        __syncwarp();
+        if (!MbarWait(sBar + buf, (uint32_t)(k / kStreamBuffers) & 1u)) {
+            failedAt = k;
+            if (lane == 0) atomicExch(&gStreamError, 1);
+            break;
+        }
+        const int live = total - k * kBatch < kBatch ? total - k * kBatch : kBatch;
+        const unsigned char *rowData = sData + (size_t)buf * kBatch * kRowBytes + lane * kLaneBytes;
+#pragma unroll 4
+        for (int j = 0; j < live; ++j) {
+            const int meta = sMeta[buf * kBatch + j];
+            const float v = sVal[buf * kBatch + j];
+            uint32_t w[kWords];
+            LaneWords<kLaneBytes>::Load(rowData + (size_t)j * kRowBytes, w);
+            float b[E];
+            WordsToF32<ValT, kWords>::Convert(w, b);
+#pragma unroll
+            for (int i = 0; i < E; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(v, b[i]));
+            if (meta & 0x100) {  // last entry of its row (warp-uniform)
+                const int l = meta & 0xff;
+                StoreSlice<OutT, E>(cRow0 + (long long)l * a.ldc, acc, old, alpha, beta);
+#pragma unroll
+                for (int i = 0; i < E; ++i) acc[i] = 0.0f;
+                const unsigned rest = l < 31 ? liveMask & (0xfffffffeu << l) : 0u;
+                if (beta != 0.0f && rest != 0) LoadOld<OutT, E>(cRow0 + (long long)(__ffs(rest) - 1) * a.ldc, old);
+            }
+        }
+        __syncwarp();  // every lane is done with this buffer before a later batch is copied into it
+    }
+    if (failedAt >= 0) {
+        // A wait ran out: this warp writes no more of C.  Give the copies still in flight (batches
+        // failedAt .. failedAt + ahead) a bounded chance to land before the shared memory they
+        // target is released.
+        for (int k = failedAt; k <= failedAt + ahead && k < nBatches; ++k)
+            (void)MbarWait(sBar + k % kStreamBuffers, (uint32_t)(k / kStreamBuffers) & 1u);
+    }
+}
+
 // ---------------------------------------------------------------- generic path
 
 struct GenericShape {
@@ -524,6 +861,33 @@ ScalarsI MakeI(const b200spScalars *s)
 
 bool Aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
+#ifndef B200SP_SPMM_USE_STREAM
+#define B200SP_SPMM_USE_STREAM 1
+#endif
+// The copy engine of an SM starts about one row copy per 20 clocks (measured: 16.8 M copies of
+// 256 bytes took 1.25 ms on 148 SMs), so rows shorter than 512 bytes move faster through plain
+// 128-bit loads and stay with SpmmFastKernel (256-byte rows, 64 per row of A: 1249 us against 265 us).
+
+template <typename ValT, typename OutT, int kRowBytes>
+int LaunchRowStream(const StreamArgs<ValT, OutT> &sa, cudaStream_t stream)
+{
+    constexpr int kSmem = StreamShape<kRowBytes>::kCtaBytes;
+    static bool configured[64] = {};  // per device: this instantiation uses kSmem bytes of dynamic shared memory
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(SpmmRowStreamKernel<ValT, OutT, kRowBytes>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+    const long long rowsPerBlock = (long long)kStreamWarps * kStreamRows;
+    const unsigned grid = (unsigned)((sa.m + rowsPerBlock - 1) / rowsPerBlock);
+    SpmmRowStreamKernel<ValT, OutT, kRowBytes><<<grid, kStreamThreads, kSmem, stream>>>(sa);
+    b200sp_note_launches(1);
+    return (int)cudaGetLastError();
+}
+
 template <typename ValT, typename OutT>
 int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, const void *B, void *C,
                 const b200spSpmmShape *sh, const b200spScalars *s, void *plan, int32_t segments,
@@ -556,7 +920,27 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
         int lanes = 1;
         while (lanes < 32 && lanes * E < sh->n) lanes <<= 1;
         const long long rowsPerBlock = (long long)kWarps * (32 / lanes);
-        const long long blocks = (long long)segments + (sh->m + rowsPerBlock - 1) / rowsPerBlock;
+        // B rows of 128 / 256 / 512 bytes: rows of up to kLongRow entries go to the row-stream kernel,
+        // and SpmmFastKernel is launched for its segment CTAs only.
+        const long long rowBytes = sh->n * (long long)sizeof(ValT);
+        const bool stream_ = !sh->kahan && (rowBytes == 512 || rowBytes == 1024) && sh->m > 0 && B200SP_SPMM_USE_STREAM;
+        if (stream_) {
+            StreamArgs<ValT, OutT> sa;
+            sa.rowPtr = rowPtr;
+            sa.colInd = colInd;
+            sa.val = a.val;
+            sa.B = a.B;
+            sa.C = a.C;
+            sa.m = a.m;
+            sa.ldb = sh->ldb;
+            sa.ldc = sh->ldc;
+            sa.sc = a.sc;
+            const int rc = rowBytes == 512 ? LaunchRowStream<ValT, OutT, 512>(sa, stream)
+                                           : LaunchRowStream<ValT, OutT, 1024>(sa, stream);
+            if (rc != 0) return rc;
+        }
+        const long long blocks =
+            (long long)segments + (stream_ ? 0 : (sh->m + rowsPerBlock - 1) / rowsPerBlock);
         if (blocks == 0) return 0;
         const unsigned grid = (unsigned)blocks;
         auto launch = [&]<int kLanes>() {
@@ -589,6 +973,13 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
 }  // namespace
 
 extern "C" {
+
+int b200sp_spmm_stream_error(void)
+{
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, gStreamError, sizeof(flag)) != cudaSuccess) return -1;
+    return flag;
+}
 
 size_t b200sp_spmm_plan_bytes(int64_t rows, int64_t nnz, int64_t n) { return LayoutFor(rows, nnz, n).total; }
 

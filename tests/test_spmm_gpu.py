@@ -1,6 +1,8 @@
 """GPU: CSR SpMM through the aclsparse C API against the CPU oracle and the golden fixtures."""
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -99,7 +101,7 @@ def test_config5_scaled(handle, device, oracle, ot):
 
 
 @pytest.mark.parametrize("vt,ot", [("f32", "f32"), ("f16", "f16"), ("bf16", "bf16"), ("bf16", "f32")])
-@pytest.mark.parametrize("n", [1, 4, 8, 24, 64, 72, 128, 200, 264, 512])
+@pytest.mark.parametrize("n", [1, 4, 8, 24, 32, 64, 72, 128, 200, 256, 264, 512])
 def test_widths_and_types(handle, device, oracle, vt, ot, n):
     rng = np.random.default_rng(n * 7 + len(vt))
     m, k = 700, 900
@@ -307,3 +309,12 @@ def test_status_codes(handle, device, pkg):
     assert L.aclsparseSpMM(handle.raw, 0, 0, None, A.raw, B.raw, al, C.raw, S.ACL_FLOAT, 0, c_void_p(buf.data_ptr())) == 0
     torch.cuda.synchronize()
     assert torch.all(C.values == 7.0)
+
+
+def test_no_wait_ran_out_in_the_row_stream_kernel(pkg, device):
+    """The row-stream kernel bounds its waits on the copy engine and raises a flag when one runs out;
+    after everything above it must still be clear.  (Runs last in this file.)"""
+    torch.cuda.synchronize()
+    f = pkg.lib().b200sp_spmm_stream_error
+    f.restype = ctypes.c_int
+    assert f() == 0
