@@ -240,17 +240,31 @@ def dtype_name(cfg) -> str:
 # DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum +
 # dram__bytes_write.sum); filled from the summaries committed under profiles/.  None = not captured.
 NCU_TRAFFIC_BYTES = {
-    "c2": 309_600_000,  # three bin kernels of one product: 147.0 + 101.2 + 61.2 MB
+    "c2": 284_459_008,  # both kernels of one product: 147.7 MB (long rows) + 136.8 MB (medium + short rows)
     "c3": 353_516_032,
     "c4": 641_619_968,
 }
 # What the counters show to be the busy resource where it is not DRAM.
 BOUND_NOTES = {
-    "c2": "x gathers from uniformly random columns: one 32-byte L2 sector request each; the L1->L2 request "
-          "port (1 per clock per SM) is 68-71 % busy, DRAM 22-25 %; floor of the formulation about 117 us",
+    "c2": "x gathers from uniformly random columns cost one 32-byte L2 sector request each and an SM issues one "
+          "request per clock: the medium + short kernel keeps that port 74 % busy (DRAM 25 %); the long rows "
+          "(56 % of the non-zeros) gather from x blocks staged in shared memory and run beside it",
     "c4": "B (67 MB) is gathered from L2: 4.48 GB through L2->L1 per product, L2 slices 71 % and L1 78 % busy",
-    "c5": "B (1.07 GB) exceeds L2: the row gather is DRAM traffic, about 17.5 GB per product (5 x algorithmic)",
+    "c5": "B (1.07 GB) exceeds L2: the row gather is DRAM traffic, about 18.8 GB per product (5.5 x the algorithmic "
+          "bytes, which count B once); against that traffic the product runs at about 6.4 TB/s",
 }
+
+
+def dominant_kernels(is_spmm: bool, launches_per_step: float, b_row_bytes: int) -> str:
+    """The kernels one step launches, as the library's routing rules give them."""
+    if is_spmm:
+        if b_row_bytes in (512, 1024):
+            return ("SpmmRowStreamKernel (rows <= 1024 nnz)" +
+                    (" + SpmmFastKernel (segment CTAs of longer rows)" if launches_per_step > 1 else ""))
+        return "SpmmFastKernel"
+    if launches_per_step > 1:
+        return "SpmvLongBlockKernel | SpmvLongListKernel (side stream) + SpmvMediumShortKernel"
+    return "SpmvShortRowsKernel | SpmvMediumShortKernel"
 
 
 def torch_dtype(kind: str):
@@ -419,9 +433,7 @@ def gpu_arm(args, synth, oracle):
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
-                "kernel": "SpmmFastKernel" if is_spmm else
-                          ("SpmvShortRowsKernel + SpmvMediumRowsKernel + SpmvLongListKernel (concurrent bins)"
-                           if launches > K else "SpmvShortRowsKernel"),
+                "kernel": dominant_kernels(is_spmm, launches / K, n * dense.element_size() if is_spmm else 0),
                 "launch_ms_mean": launch_ms_mean,
                 "algorithmic_bytes_per_launch": my_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.config) if world == 1 else None,
                 "note": BOUND_NOTES.get(args.config),
