@@ -191,12 +191,20 @@ class CpuGolden:
 
 def cpu_baseline(cfg, oracle, threads: int, budget_s: float = 12.0) -> dict:
     """At most about `budget_s` seconds of wall time on all host threads: the whole matrix when a pass is
-    short (repeated until about a second has been spent), else its leading rows, 3 passes."""
+    short (repeated until about a second has been spent), else its leading rows, 3 passes.  The same loop
+    on one thread (the golden as the reference's harness runs it) is timed beside it on a sample a
+    tenth as long."""
     g = CpuGolden(cfg, oracle, threads)
     rows = g.rows_for(budget_s / 3)
     sec, _ = g.run(rows, 1)  # also the warm-up pass
     reps = int(min(200, max(3, round(1.0 / max(sec, 1e-4)))))
-    return g.report(rows, reps)
+    rep = g.report(rows, reps)
+    one = CpuGolden(cfg, oracle, 1)
+    rows1 = one.rows_for(budget_s / 30)
+    one.run(rows1, 1)
+    r1 = one.report(rows1, 3)
+    rep["single_core"] = {"value": r1["value"], "unit": r1["unit"], "sample": r1["sample"]}
+    return rep
 
 
 def reference_arm(args, synth, oracle):
@@ -445,7 +453,8 @@ def gpu_arm(args, synth, oracle):
             "gpu_launches": launches * world, "kernels_per_step": launches / K, "clocks": clocks, "parity_spot_check": parity_ok,
         }
         if base is not None:
-            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "single_core")
+                                    if k in base}
         print(json.dumps(line))
     op.close()
     if world > 1:
