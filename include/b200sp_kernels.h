@@ -116,6 +116,34 @@ int b200sp_spmv_f32_noalloc(const int32_t *row_ptr, const int32_t *col_ind, cons
                             float *y, int64_t rows, int64_t cols, int64_t nnz, float alpha, float beta,
                             void *stream);
 
+/* ------------------------------------------------------------------ SpMVOp ----------- */
+
+/* Number of row-length classes the SpMVOp analysis sorts rows into (class c holds the rows whose
+ * length needs c bits: 0, 1, 2-3, 4-7, ...). */
+#define B200SP_SPMVOP_CLASSES 33
+
+/* Bytes of workspace for b200sp_spmvop_analyze on a matrix of `rows` rows. */
+size_t b200sp_spmvop_plan_bytes(int64_t rows);
+
+/* Orders the rows by descending length class into `plan` (a permutation of 0..rows-1) and writes to
+ * class_start[c], c = 0..B200SP_SPMVOP_CLASSES, where the rows of class (CLASSES - 1 - c) start in it
+ * (class_start[CLASSES] = rows).  row_offsets is int32 or int64 (offsets_are_64).  Synchronises
+ * `stream` once.  Counterpart of the reference's spmv_op_preprocess_kernel_do. */
+int b200sp_spmvop_analyze(const void *row_offsets, int offsets_are_64, int64_t rows, void *plan, size_t plan_bytes,
+                          int32_t *class_start, void *stream);
+
+/* z = alpha * A * x + beta * y, fp32, doubly compensated row sums.  index_base is 0 or 1.  alpha_dev /
+ * beta_dev, when not NULL, are device pointers that replace alpha / beta.  With plan == NULL every row
+ * gets the same number of lanes (chosen from nnz / rows); with a plan from b200sp_spmvop_analyze each
+ * length class gets its own.  z may be y.  Counterpart of the reference's spmv_op_kernel_do. */
+int b200sp_spmvop_launch(const void *row_offsets, int offsets_are_64, const int32_t *col_ind, const float *val,
+                         const float *x, const float *y, float *z, int64_t rows, int64_t nnz, int index_base,
+                         float alpha, float beta, const float *alpha_dev, const float *beta_dev, const void *plan,
+                         const int32_t *class_start, void *stream);
+
+/* z = beta * y (beta == 0: zeros, y not read).  Counterpart of spmv_op_beta_y_kernel_do. */
+int b200sp_spmvop_scale(const float *y, float *z, int64_t rows, float beta, const float *beta_dev, void *stream);
+
 /* ------------------------------------------------------------------ SpMM ------------- */
 
 /* Dense operand layout, same meaning as the reference's SpmmTilingData

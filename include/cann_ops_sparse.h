@@ -89,7 +89,22 @@ typedef enum aclsparsePointerMode_t {
     ACL_SPARSE_POINTER_MODE_DEVICE = 1
 } aclsparsePointerMode_t;
 
-/* ---- opaque types (reference :30-47) ---- */
+/* Algorithms of the SpMVOp plan API (reference include/cann_ops_sparse.h:55-70).  DEFAULT routes to
+ * ALG1.  ALG1 needs no workspace; ALG2 orders the rows by length in createDescr and needs the
+ * workspace that aclsparseSpMVOp_bufferSize reports.  Neither looks at the values of A, so csrValues
+ * may be updated in place under both (the reference forbids that under its ALG2). */
+typedef enum aclsparseSpMVOpAlg_t {
+    ACL_SPARSE_SPMVOP_ALG_DEFAULT = 0,
+    ACL_SPARSE_SPMVOP_ALG1,
+    ACL_SPARSE_SPMVOP_ALG2
+} aclsparseSpMVOpAlg_t;
+
+/* ---- opaque types (reference :30-47, 72-78) ---- */
+struct aclsparseSpMVOpDescr;
+struct aclsparseSpMVOpPlan;
+typedef struct aclsparseSpMVOpDescr *aclsparseSpMVOpDescr_t;
+typedef struct aclsparseSpMVOpDescr const *aclsparseConstSpMVOpDescr_t;
+typedef struct aclsparseSpMVOpPlan *aclsparseSpMVOpPlan_t;
 struct aclsparseContext;
 struct aclsparseSpMatDescr;
 struct aclsparseDnVecDescr;
@@ -235,6 +250,35 @@ aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t o
                                 const void *alpha, aclsparseConstSpMatDescr_t matA,
                                 aclsparseConstDnMatDescr_t matB, const void *beta, aclsparseDnMatDescr_t matC,
                                 aclDataType computeType, aclsparseSpMMAlg_t alg, void *buffer);
+
+/* ---- SpMVOp plan API: Z = alpha * A * X + beta * Y (reference include/cann_ops_sparse.h:1564-1637,
+ * sparse/spmv_op/arch35/spmv_op_host.cpp:496-745).  fp32 only, opA = NON_TRANSPOSE only, CSR with int32
+ * column indices, int32 or int64 row offsets, index base 0 or 1; X has exactly cols entries, Y and Z
+ * exactly rows; Z may be Y.  Every row is summed with the doubly compensated dot product of the
+ * reference kernel (spmv_op_kernel.cpp:88-127) on a fixed reduction shape, so results are reproducible
+ * bit for bit.  alpha and beta are required and follow the handle's pointer mode; with beta == 0, Y is
+ * not read.  The epilogue arguments exist for signature compatibility: a non-NULL epilogue buffer is
+ * NOT_SUPPORTED, setGlobalUserData checks its arguments and does nothing. ---- */
+aclsparseStatus_t aclsparseSpMVOp_bufferSize(aclsparseHandle_t handle, aclsparseOperation_t opA,
+                                             aclsparseConstSpMatDescr_t matA, aclsparseConstDnVecDescr_t vecX,
+                                             aclsparseConstDnVecDescr_t vecY, aclsparseDnVecDescr_t vecZ,
+                                             aclDataType computeType, aclsparseSpMVOpAlg_t alg, size_t *bufferSize);
+aclsparseStatus_t aclsparseSpMVOp_createDescr(aclsparseHandle_t handle, aclsparseSpMVOpDescr_t *descr,
+                                              aclsparseOperation_t opA, aclsparseConstSpMatDescr_t matA,
+                                              aclsparseConstDnVecDescr_t vecX, aclsparseConstDnVecDescr_t vecY,
+                                              aclsparseDnVecDescr_t vecZ, aclDataType computeType,
+                                              aclsparseSpMVOpAlg_t alg, void *buffer);
+aclsparseStatus_t aclsparseSpMVOp_destroyDescr(aclsparseSpMVOpDescr_t descr);
+aclsparseStatus_t aclsparseSpMVOp_createPlan(aclsparseHandle_t handle, aclsparseSpMVOpDescr_t descr,
+                                             aclsparseSpMVOpPlan_t *plan, const void *epilogueLTOBuffer,
+                                             size_t epilogueLTOBufferSize);
+aclsparseStatus_t aclsparseSpMVOp_destroyPlan(aclsparseSpMVOpPlan_t plan);
+aclsparseStatus_t aclsparseSpMVOp_setGlobalUserData(aclsparseHandle_t handle, aclsparseSpMVOpPlan_t plan,
+                                                    const char *epilogueDataName, void *epilogueData,
+                                                    size_t epilogueDataSize);
+aclsparseStatus_t aclsparseSpMVOp(aclsparseHandle_t handle, aclsparseSpMVOpPlan_t plan, const void *alpha,
+                                  const void *beta, aclsparseConstDnVecDescr_t vecX,
+                                  aclsparseConstDnVecDescr_t vecY, aclsparseDnVecDescr_t vecZ);
 
 #ifdef __cplusplus
 }

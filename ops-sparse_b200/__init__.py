@@ -27,6 +27,7 @@ ACL_SPARSE_OP_NON_TRANSPOSE, ACL_SPARSE_OP_TRANSPOSE, ACL_SPARSE_OP_CONJUGATE_TR
 ACL_SPARSE_ORDER_ROW, ACL_SPARSE_ORDER_COL = 0, 1
 ACL_SPARSE_SPMM_ALG_DEFAULT, ACL_SPARSE_SPMM_CSR_ALG1, ACL_SPARSE_SPMM_CSR_FP32_HIGH_PRECISION_ALG = 0, 1, 2
 ACL_SPARSE_SPMV_ALG_DEFAULT, ACL_SPARSE_SPMV_CSR_ALG1 = 0, 3
+ACL_SPARSE_SPMVOP_ALG_DEFAULT, ACL_SPARSE_SPMVOP_ALG1, ACL_SPARSE_SPMVOP_ALG2 = 0, 1, 2
 ACL_SPARSE_INDEX_32I, ACL_SPARSE_INDEX_64I = 0, 1
 ACL_SPARSE_INDEX_BASE_ZERO, ACL_SPARSE_INDEX_BASE_ONE = 0, 1
 ACL_SPARSE_FORMAT_COO, ACL_SPARSE_FORMAT_CSR, ACL_SPARSE_FORMAT_CSC = 0, 1, 2
@@ -104,6 +105,14 @@ _SIGNATURES = {
     "aclsparseSpMMGetBufferSize": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, POINTER(c_size_t)],
     "aclsparseSpMMPreprocess": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P],
     "aclsparseSpMM": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P],
+    # SpMVOp plan API
+    "aclsparseSpMVOp_bufferSize": [P, c_int, P, P, P, P, c_int, c_int, POINTER(c_size_t)],
+    "aclsparseSpMVOp_createDescr": [P, POINTER(P), c_int, P, P, P, P, c_int, c_int, P],
+    "aclsparseSpMVOp_destroyDescr": [P],
+    "aclsparseSpMVOp_createPlan": [P, P, POINTER(P), P, c_size_t],
+    "aclsparseSpMVOp_destroyPlan": [P],
+    "aclsparseSpMVOp_setGlobalUserData": [P, P, ctypes.c_char_p, P, c_size_t],
+    "aclsparseSpMVOp": [P, P, P, P, P, P, P],
     # multi-GPU helpers (include/b200sp_mg.h)
     "b200spMgPartitionRows": [P, c_int64, c_int32, POINTER(c_int64)],
 }

@@ -14,7 +14,8 @@ from ctypes import byref, c_float, c_int, c_int32, c_size_t, c_void_p
 import torch
 
 from . import (
-    ACL_BF16, ACL_FLOAT, ACL_FLOAT16, ACL_INT8, ACL_INT32, ACL_SPARSE_INDEX_32I, ACL_SPARSE_INDEX_BASE_ZERO,
+    ACL_BF16, ACL_FLOAT, ACL_FLOAT16, ACL_INT8, ACL_INT32, ACL_SPARSE_INDEX_32I, ACL_SPARSE_INDEX_64I,
+    ACL_SPARSE_INDEX_BASE_ZERO, ACL_SPARSE_SPMVOP_ALG_DEFAULT, ACL_SPARSE_SPMVOP_ALG2,
     ACL_SPARSE_OP_NON_TRANSPOSE, ACL_SPARSE_ORDER_COL, ACL_SPARSE_ORDER_ROW, ACL_SPARSE_POINTER_MODE_DEVICE,
     ACL_SPARSE_SPMM_ALG_DEFAULT, ACL_SPARSE_SPMV_ALG_DEFAULT, check, lib,
 )
@@ -128,15 +129,17 @@ class DnMat:
 
 class CsrMatrix:
     def __init__(self, row_ptr: torch.Tensor, col_ind: torch.Tensor, values: torch.Tensor, rows: int, cols: int,
-                 nnz: int | None = None):
-        assert row_ptr.dtype == torch.int32 and col_ind.dtype == torch.int32
+                 nnz: int | None = None, index_base: int = ACL_SPARSE_INDEX_BASE_ZERO):
+        """row_ptr is int32, or int64 for the SpMVOp plan API; index_base 1 likewise is SpMVOp only."""
+        assert row_ptr.dtype in (torch.int32, torch.int64) and col_ind.dtype == torch.int32
         self.row_ptr, self.col_ind, self.values = row_ptr, col_ind, values
         self.rows, self.cols = rows, cols
         self.nnz = col_ind.numel() if nnz is None else nnz
         self._d = c_void_p()
+        off_type = ACL_SPARSE_INDEX_64I if row_ptr.dtype == torch.int64 else ACL_SPARSE_INDEX_32I
         check(lib().aclsparseCreateCsr(byref(self._d), rows, cols, self.nnz, _ptr(row_ptr), _ptr(col_ind),
-                                       _ptr(values), ACL_SPARSE_INDEX_32I, ACL_SPARSE_INDEX_32I,
-                                       ACL_SPARSE_INDEX_BASE_ZERO, acl_type_of(values.dtype)),
+                                       _ptr(values), off_type, ACL_SPARSE_INDEX_32I, index_base,
+                                       acl_type_of(values.dtype)),
               "aclsparseCreateCsr")
         self.buffer: torch.Tensor | None = None  # workspace recorded by preprocess_*()
 
@@ -229,3 +232,47 @@ def spmm(handle: Handle, A: CsrMatrix, B: DnMat, C: DnMat, alpha=1.0, beta=0.0,
     check(lib().aclsparseSpMM(handle.raw, ACL_SPARSE_OP_NON_TRANSPOSE, op_b, a, A.raw, B.raw, b, C.raw, ct, alg,
                               _ptr(buf)), "aclsparseSpMM")
     del keep
+
+
+class SpMVOpPlan:
+    """aclsparseSpMVOp_bufferSize -> createDescr -> createPlan for one matrix; `run` is aclsparseSpMVOp.
+
+    Z = alpha * A * X + beta * Y in fp32 with compensated row sums; Z may be Y.  The workspace of ALG2
+    is owned by this object and lives as long as it does.
+    """
+
+    def __init__(self, handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, z: DnVec,
+                 alg: int = ACL_SPARSE_SPMVOP_ALG_DEFAULT):
+        self.handle, self.A = handle, A
+        size = c_size_t()
+        check(lib().aclsparseSpMVOp_bufferSize(handle.raw, ACL_SPARSE_OP_NON_TRANSPOSE, A.raw, x.raw, y.raw, z.raw,
+                                               ACL_FLOAT, alg, byref(size)), "aclsparseSpMVOp_bufferSize")
+        self.buffer_bytes = size.value
+        self.buffer = (torch.empty(max(size.value, 1), dtype=torch.uint8, device=A.col_ind.device)
+                       if alg == ACL_SPARSE_SPMVOP_ALG2 else None)
+        self._descr, self._plan = c_void_p(), c_void_p()
+        check(lib().aclsparseSpMVOp_createDescr(handle.raw, byref(self._descr), ACL_SPARSE_OP_NON_TRANSPOSE, A.raw,
+                                                x.raw, y.raw, z.raw, ACL_FLOAT, alg,
+                                                _ptr(self.buffer) if self.buffer is not None else None),
+              "aclsparseSpMVOp_createDescr")
+        check(lib().aclsparseSpMVOp_createPlan(handle.raw, self._descr, byref(self._plan), None, 0),
+              "aclsparseSpMVOp_createPlan")
+
+    def run(self, x: DnVec, y: DnVec, z: DnVec, alpha=1.0, beta=0.0) -> None:
+        a, b, keep = _scalars(self.handle, alpha, beta, ACL_FLOAT)
+        check(lib().aclsparseSpMVOp(self.handle.raw, self._plan, a, b, x.raw, y.raw, z.raw), "aclsparseSpMVOp")
+        del keep
+
+    def close(self) -> None:
+        if self._plan:
+            lib().aclsparseSpMVOp_destroyPlan(self._plan)
+            self._plan = c_void_p()
+        if self._descr:
+            lib().aclsparseSpMVOp_destroyDescr(self._descr)
+            self._descr = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -26,6 +26,8 @@ SOURCES = [
     "common/descr.cpp",
     "spmv/spmv_host.cpp",
     "spmv/spmv_kernels.cu",
+    "spmv_op/spmv_op_host.cpp",
+    "spmv_op/spmv_op_kernels.cu",
     "spmm/spmm_host.cpp",
     "spmm/spmm_kernels.cu",
     "mg/partition.cpp",

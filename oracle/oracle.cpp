@@ -445,6 +445,46 @@ int64_t oracle_verify_abs_and_rel(const float *got, const float *gold, int64_t c
     return errors;
 }
 
+// SpMVOp: Z = alpha * A * X + beta * Y, one row at a time in CSR order with Priest's doubly compensated dot
+// product, restated from the reference's device code (sparse/spmv_op/arch35/spmv_op_kernel.cpp:88-127 for the
+// recurrence, :157-180 for the row bounds, the beta == 0 short cut and the final combination).  row_offsets is
+// int32 or int64; index_base is subtracted from offsets and columns alike.  Parity of this restatement is
+// unpinned: the reference code is AscendC device code that does not compile here, and its own golden
+// (test/spmv_op/spmv_op_golden.h) needs Eigen, which is absent; the tests check it against an exact (fp64)
+// product within the error bound the reference states for the algorithm and with the reference test table's
+// criteria.
+void oracle_spmv_op(const void *row_offsets, int offsets_are_64, const int32_t *col_ind, const float *val,
+                    const float *x, const float *y, float *z, int64_t rows, int index_base, float alpha, float beta)
+{
+    auto offset = [&](int64_t i) -> int64_t {
+        return offsets_are_64 ? static_cast<const int64_t *>(row_offsets)[i]
+                              : (int64_t)static_cast<const int32_t *>(row_offsets)[i];
+    };
+    for (int64_t r = 0; r < rows; ++r) {
+        const int64_t s = offset(r) - index_base, e = offset(r + 1) - index_base;
+        float hi = 0.0f, md = 0.0f, lo = 0.0f;
+        for (int64_t p = s; p < e; ++p) {
+            const float v = val[p], xv = x[col_ind[p] - index_base];
+            const float prod = v * xv;
+            const float pi = std::fmaf(v, xv, -prod);
+            const float s1 = hi + prod;
+            const float v1 = s1 - hi;
+            const float e1 = (hi - (s1 - v1)) + (prod - v1);
+            hi = s1;
+            const float ee = e1 + pi;
+            const float s2 = md + ee;
+            const float v2 = s2 - md;
+            const float e2 = (md - (s2 - v2)) + (ee - v2);
+            md = s2;
+            lo = lo + e2;
+        }
+        const float yv = beta == 0.0f ? 0.0f : y[r];
+        const float corr = md + lo;
+        const float step1 = std::fmaf(alpha, corr, beta * yv);
+        z[r] = std::fmaf(alpha, hi, step1);
+    }
+}
+
 int oracle_hardware_threads(void)
 {
     const unsigned n = std::thread::hardware_concurrency();

@@ -198,6 +198,38 @@ MIXED_TOL = {  # rtol, atol, max-abs-error limit, required matched ratio (spmv_t
 }
 
 
+def spmv_op(row_offsets, col_ind, val, x, y, alpha, beta, index_base=0) -> np.ndarray:
+    """Z = alpha A X + beta Y with the reference's doubly compensated row sums (fp32); row_offsets int32 or int64."""
+    ro = np.ascontiguousarray(row_offsets)
+    assert ro.dtype in (np.int32, np.int64)
+    rows = ro.size - 1
+    ci, v = _c(col_ind, np.int32), _c(val, np.float32)
+    xx, yy = _c(x, np.float32), _c(y, np.float32)
+    z = np.empty(rows, np.float32)
+    f = lib().oracle_spmv_op
+    f.restype = None
+    f.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                  ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_float]
+    f(_p(ro), int(ro.dtype == np.int64), _p(ci), _p(v), _p(xx), _p(yy), _p(z), rows, int(index_base), float(alpha),
+      float(beta))
+    return z
+
+
+def spmv_exact(row_offsets, col_ind, val, x, y, alpha, beta, index_base=0):
+    """(alpha A x + beta y, sum_j |a_ij x_j|) in fp64 from fp32 inputs: the products are exact in fp64, the sums
+    are not, but their error is far below fp32 resolution for the sizes the tests use."""
+    ro = np.asarray(row_offsets, np.int64) - index_base
+    ci = np.asarray(col_ind, np.int64) - index_base
+    prod = np.asarray(val, np.float64) * np.asarray(x, np.float64)[ci]
+    rows = ro.size - 1
+    seg = np.repeat(np.arange(rows), np.diff(ro))
+    dot = np.bincount(seg, weights=prod, minlength=rows)[:rows]
+    mag = np.bincount(seg, weights=np.abs(prod), minlength=rows)[:rows]
+    yy = np.asarray(y, np.float64)
+    z = np.float64(np.float32(alpha)) * dot + (np.float64(np.float32(beta)) * yy if beta != 0 else 0.0)
+    return z, mag
+
+
 def verify_mixed(gold, got, kind="f32"):
     rtol, atol, limit, ratio = MIXED_TOL[kind]
     gold, got = _c(gold, np.float32).ravel(), _c(got, np.float32).ravel()
