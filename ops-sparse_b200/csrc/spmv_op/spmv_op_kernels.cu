@@ -14,7 +14,8 @@
 // Two ways to pick G:
 //   no plan (ALG1)   one G for the whole matrix, from nnz / rows; nothing is analysed;
 //   plan (ALG2)      the analysis orders the rows by descending length class (class c: lengths that
-//                    need c bits) and each class range gets its own G, longest rows first -- the
+//                    need c bits); rows of 1024 entries and more get a CTA each, every other class
+//                    range its own G, longest rows first -- the
 //                    counterpart of the reference's reorder / bin_edge tables
 //                    (spmv_op_kernel.cpp:425-540), built here by a histogram and a scatter.
 #include <cstdint>
@@ -122,7 +123,20 @@ __global__ void __launch_bounds__(256) SpmvOpRowsKernel(const OpArgs a)
         float yOld = 0.0f;
         if (live && lane == 0 && beta != 0.0f) yOld = a.y[row];  // requested now, used at the end
         Triple t{0.0f, 0.0f, 0.0f};
-        for (long long p = s + lane; p < e; p += G) {
+        // Four entries are requested before the first of them is used; the steps run in entry order.
+        long long p = s + lane;
+        for (; p + 3 * G < e; p += 4 * G) {
+            float v[4], xv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int col = __ldcs(a.colInd + p + u * G) - a.indexBase;
+                v[u] = __ldcs(a.val + p + u * G);
+                xv[u] = __ldg(a.x + col);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) PriestStep(t, v[u], xv[u]);
+        }
+        for (; p < e; p += G) {
             const int col = __ldcs(a.colInd + p) - a.indexBase;
             PriestStep(t, __ldcs(a.val + p), __ldg(a.x + col));
         }
@@ -139,6 +153,67 @@ __global__ void __launch_bounds__(256) SpmvOpRowsKernel(const OpArgs a)
             const float corr = __fadd_rn(t.md, t.lo);
             const float step1 = __fmaf_rn(alpha, corr, __fmul_rn(beta, yOld));
             a.z[row] = __fmaf_rn(alpha, t.hi, step1);
+        }
+    }
+}
+
+// Rows of kLongBits bits or more (1024 entries and up): one CTA per row.  Thread t runs the recurrence on
+// entries t, t + 256, ...; the lanes of a warp are joined on the butterfly, then warp 0 joins the eight
+// warp triples the same way: a fixed shape again.
+constexpr int kLongBits = 11;
+template <bool kIs64>
+__global__ void __launch_bounds__(256) SpmvOpLongRowsKernel(const OpArgs a)
+{
+    __shared__ Triple sWarp[8];
+    const float alpha = a.alphaDev ? *a.alphaDev : a.alpha;
+    const float beta = a.betaDev ? *a.betaDev : a.beta;
+    const int tid = threadIdx.x;
+    const long long row = a.reorder ? (long long)a.reorder[a.first + blockIdx.x] : a.first + blockIdx.x;
+    const long long s = LoadOffset(a.rowOffsets, kIs64, row) - a.indexBase;
+    const long long e = LoadOffset(a.rowOffsets, kIs64, row + 1) - a.indexBase;
+    float yOld = 0.0f;
+    if (tid == 0 && beta != 0.0f) yOld = a.y[row];
+    Triple t{0.0f, 0.0f, 0.0f};
+    long long p = s + tid;
+    for (; p + 3 * 256 < e; p += 4 * 256) {
+        float v[4], xv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int col = __ldcs(a.colInd + p + u * 256) - a.indexBase;
+            v[u] = __ldcs(a.val + p + u * 256);
+            xv[u] = __ldg(a.x + col);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) PriestStep(t, v[u], xv[u]);
+    }
+    for (; p < e; p += 256) {
+        const int col = __ldcs(a.colInd + p) - a.indexBase;
+        PriestStep(t, __ldcs(a.val + p), __ldg(a.x + col));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        Triple o;
+        o.hi = __shfl_down_sync(0xffffffffu, t.hi, off);
+        o.md = __shfl_down_sync(0xffffffffu, t.md, off);
+        o.lo = __shfl_down_sync(0xffffffffu, t.lo, off);
+        JoinTriples(t, o);
+    }
+    if ((tid & 31) == 0) sWarp[tid >> 5] = t;
+    __syncthreads();
+    if (tid < 32) {
+        Triple w = tid < 8 ? sWarp[tid] : Triple{0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) {
+            Triple o;
+            o.hi = __shfl_down_sync(0xffffffffu, w.hi, off);
+            o.md = __shfl_down_sync(0xffffffffu, w.md, off);
+            o.lo = __shfl_down_sync(0xffffffffu, w.lo, off);
+            JoinTriples(w, o);
+        }
+        if (tid == 0) {
+            const float corr = __fadd_rn(w.md, w.lo);
+            const float step1 = __fmaf_rn(alpha, corr, __fmul_rn(beta, yOld));
+            a.z[row] = __fmaf_rn(alpha, w.hi, step1);
         }
     }
 }
@@ -317,8 +392,16 @@ int b200sp_spmvop_launch(const void *row_offsets, int offsets_are_64, const int3
         return (int)cudaGetLastError();
     }
     a.reorder = static_cast<const int32_t *>(plan);
-    // One launch per run of classes that share a lane count, longest rows first.
-    int k = 0;
+    // Classes of kLongBits bits and more: a CTA per row.
+    int k = kClasses - kLongBits;  // class_start index of class kLongBits - 1
+    a.first = class_start[0];
+    a.count = (long long)class_start[k] - class_start[0];
+    if (a.count > 0) {
+        if (offsets_are_64) SpmvOpLongRowsKernel<true><<<(unsigned)a.count, 256, 0, st>>>(a);
+        else SpmvOpLongRowsKernel<false><<<(unsigned)a.count, 256, 0, st>>>(a);
+        b200sp_note_launches(1);
+    }
+    // Then one launch per run of classes that share a lane count, longest rows first.
     while (k < kClasses) {
         const int G = LanesForClass(kClasses - 1 - k);
         int k2 = k;
