@@ -376,22 +376,34 @@ def gpu_arm(args, synth, oracle):
     torch.cuda.synchronize()
     launch_ms_mean = max_over_ranks(e0.elapsed_time(e1) / KL)
 
-    # ---- end to end: host buffers in, host result out, every step
+    # ---- end to end: host buffers in, host result out, every step.  The package's host-operand API cuts the
+    # rows into panels so that the copies of one panel overlap the product of another.
+    from ops_sparse_b200 import hostio
     KE = min(K, 200)
+    pipe = hostio.HostOperandProduct(rp, d_ci, d_v, A.cols, dense, out, panels=args.e2e_panels)
+    graph = pipe.capture(dense_h, out_h, result_h, alpha, beta) if (world == 1 and not args.no_graph) else None
+
+    def e2e_step():
+        if graph is not None:
+            graph.replay()  # the recorded step: x / B up, per panel y / C up -> product -> result down
+        else:
+            pipe.step(dense_h, out_h, result_h, alpha, beta, upload_dense=(rank == 0))
+
+    for _ in range(3):
+        e2e_step()
     barrier()
     e0.record()
     for _ in range(KE):
-        if rank == 0:
-            dense.copy_(dense_h, non_blocking=True)
-        out.copy_(out_h, non_blocking=True)
-        step()
-        result_h.copy_(out, non_blocking=True)
+        e2e_step()
         torch.cuda.synchronize()  # the caller needs the result before the next step
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / KE
-    h2d = dense_h.numel() * dense_h.element_size() + A.rows * n * out_h.element_size()
-    d2h = A.rows * n * out_h.element_size()
+    pipe.close()
+    # bytes this rank moves per step (rank 0 also uploads x / B; y / C goes up only when beta != 0 reads it)
+    out_bytes = (r1 - r0) * n * out_h.element_size()
+    h2d = (dense_h.numel() * dense_h.element_size() if rank == 0 else 0) + (out_bytes if beta != 0 else 0)
+    d2h = out_bytes
 
     # ---- spot check of the last end-to-end result against the CPU oracle (first local rows)
     check_rows = min(r1 - r0, 20000 if not is_spmm else 512)
@@ -447,7 +459,8 @@ def gpu_arm(args, synth, oracle):
                 "note": BOUND_NOTES.get(args.config),
             },
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE},
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE,
+                    "row_panels": args.e2e_panels, "cuda_graph": graph is not None},
             "compute_only": {"value": flops / (launch_ms_mean * 1e-3) / 1e9, "unit": "GFLOP/s",
                              "note": "max-over-ranks mean launch time, no broadcast"},
             "gpu_launches": launches * world, "kernels_per_step": launches / K, "clocks": clocks, "parity_spot_check": parity_ok,
@@ -471,6 +484,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU golden timing leg")
+    ap.add_argument("--no-graph", action="store_true", help="end-to-end leg: issue every step's operations one by one")
+    ap.add_argument("--e2e-panels", type=int, default=4,
+                    help="row panels the end-to-end leg pipelines its host copies over (1 = copy, compute, copy)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     entry.load_package()
