@@ -17,7 +17,7 @@
 //                           of rows adds their per-block partial sums in block order.
 //   SpmvLongListKernel      (otherwise) one CTA per listed row, 128-bit loads.
 //   SpmvMediumShortKernel   one grid: first a warp per listed medium row, then every row gets
-//                           a group of G = 2, 4 or 8 lanes (rows longer than 32 entries are
+//                           a group of G = 2 or 4 lanes (rows longer than 32 entries are
 //                           skipped).  SpmvShortRowsKernel alone when no row is medium.
 // Gathers of x from scattered columns cost one L2 sector request each, and an SM issues one
 // request per clock: many light warps, each with a few independent gathers in flight, keep
@@ -402,7 +402,7 @@ __global__ void __launch_bounds__(kTileThreads, B200SP_SPMV_MIN_BLOCKS) SpmvTile
 // ---------------------------------------------------------------- binned path
 
 // Rows are binned by length by the analysis pass and each bin has its own code:
-//   short  (<= kShortMax entries)   ShortRowsBody : G = 2, 4 or 8 lanes per row, all rows scanned
+//   short  (<= kShortMax entries)   ShortRowsBody : G = 2 or 4 lanes per row (8 compiles, for experiments), all rows scanned
 //   medium (<  kLongLen entries)    MediumRowsBody: one warp per listed row
 //   long   (>= kLongLen entries)    SpmvLongBlockKernel (x blocks in shared memory) or LongRowBody (a CTA per row)
 // Short and medium rows share one grid; the long rows run beside it on a side stream.
@@ -1352,7 +1352,9 @@ int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t 
 #ifdef B200SP_SPMV_FORCE_SHORT_G
     plan_info[kInfoGroup] = B200SP_SPMV_FORCE_SHORT_G;
 #else
-    plan_info[kInfoGroup] = avgShort < 6.0 ? 2 : (avgShort < 24.0 ? 4 : 8);
+    // measured: 27-entry stencil rows run 92 us with 2 or 4 lanes per row, 107 us with 8, 141 us with 16;
+    // power-law rows (3.3 entries on average) 96 us with 2 lanes, 115 us with 4
+    plan_info[kInfoGroup] = avgShort < 6.0 ? 2 : 4;
 #endif
     return 0;
 }
