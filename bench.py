@@ -365,8 +365,8 @@ def gpu_arm(args, synth, oracle):
     ms_per_step = total_ms / K
 
     # ---- compute-only steps (no broadcast): launch duration for the roofline.  A step is one
-    # launch of the dominant kernel (plus, for the binned SpMV, its two sibling kernels running
-    # beside it on side streams), so the duration is the event-bracketed region divided by the steps.
+    # launch of the dominant kernel (plus, for the binned SpMV, the long-row kernel running beside
+    # it on a side stream), so the duration is the event-bracketed region divided by the steps.
     KL = min(K, 200)
     barrier()
     e0.record()
@@ -462,7 +462,11 @@ def gpu_arm(args, synth, oracle):
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE,
                     "row_panels": args.e2e_panels, "cuda_graph": graph is not None},
             "compute_only": {"value": flops / (launch_ms_mean * 1e-3) / 1e9, "unit": "GFLOP/s",
-                             "note": "max-over-ranks mean launch time, no broadcast"},
+                             "ms_per_step": launch_ms_mean,
+                             "broadcast_ms_per_step": max(ms_per_step - launch_ms_mean, 0.0) if world > 1 else 0.0,
+                             "note": "max-over-ranks mean product time without the broadcast (an event after "
+                                     "every single step would add its own 15-30 us to a 95 us step, so no "
+                                     "per-step spread is reported)"},
             "gpu_launches": launches * world, "kernels_per_step": launches / K, "clocks": clocks, "parity_spot_check": parity_ok,
         }
         if base is not None:

@@ -280,6 +280,13 @@ aclsparseStatus_t aclsparseSpMVOp(aclsparseHandle_t handle, aclsparseSpMVOpPlan_
                                   const void *beta, aclsparseConstDnVecDescr_t vecX,
                                   aclsparseConstDnVecDescr_t vecY, aclsparseDnVecDescr_t vecZ);
 
+/* ---- COO row indices -> CSR row offsets (reference include/cann_ops_sparse.h:1796-1822,
+ * sparse/coo2csr/arch35/coo2csr_host.cpp:38-78).  cooRowInd[0..nnz) is sorted non-decreasing, DEVICE;
+ * csrRowPtr[0..m] is written, DEVICE; both carry the index base.  The step before the products in
+ * pipelines that assemble A as triplets. ---- */
+aclsparseStatus_t aclsparseXcoo2csr(aclsparseHandle_t handle, const int *cooRowInd, int nnz, int m, int *csrRowPtr,
+                                    aclsparseIndexBase_t idxBase);
+
 #ifdef __cplusplus
 }
 #endif

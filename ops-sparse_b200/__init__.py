@@ -113,6 +113,7 @@ _SIGNATURES = {
     "aclsparseSpMVOp_destroyPlan": [P],
     "aclsparseSpMVOp_setGlobalUserData": [P, P, ctypes.c_char_p, P, c_size_t],
     "aclsparseSpMVOp": [P, P, P, P, P, P, P],
+    "aclsparseXcoo2csr": [P, P, c_int, c_int, P, c_int],
     # multi-GPU helpers (include/b200sp_mg.h)
     "b200spMgPartitionRows": [P, c_int64, c_int32, POINTER(c_int64)],
 }

@@ -28,6 +28,7 @@ SOURCES = [
     "spmv/spmv_kernels.cu",
     "spmv_op/spmv_op_host.cpp",
     "spmv_op/spmv_op_kernels.cu",
+    "convert/coo2csr.cu",
     "spmm/spmm_host.cpp",
     "spmm/spmm_kernels.cu",
     "mg/partition.cpp",

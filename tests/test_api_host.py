@@ -199,3 +199,20 @@ def test_buffer_size_formulas(pkg):
     blocked = bins + (nnz // 1024 + 1) * (2 * xb + 1) * 4 + 256
     assert blocked <= L.b200sp_spmv_plan_bytes(rows, rows, nnz) <= blocked + 2048
     assert L.b200sp_spmm_plan_bytes(1 << 18, 1 << 24, 64) >= 2 * ((1 << 24) // 4096) * 64 * 4
+
+
+def test_coo2csr_argument_checks_without_device(pkg):
+    """Order and codes of sparse/coo2csr/arch35/coo2csr_host.cpp:38-78; every case returns before any launch."""
+    L, S = pkg.lib(), pkg
+    H = c_void_p(0x10)
+    f = L.aclsparseXcoo2csr
+    INV = S.ACL_SPARSE_STATUS_INVALID_VALUE
+    assert f(None, FAKE, 4, 4, FAKE, 0) == S.ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR
+    assert f(H, FAKE, -1, 4, FAKE, 0) == INV
+    assert f(H, FAKE, 2 ** 31 - 1, 4, FAKE, 1) == INV      # nnz + base would overflow
+    assert f(H, FAKE, 4, -1, FAKE, 0) == INV
+    assert f(H, FAKE, 4, 0, FAKE, 0) == INV                # entries but no rows
+    assert f(H, FAKE, 4, 4, FAKE, 2) == INV                # index base
+    assert f(H, None, 4, 4, FAKE, 0) == INV
+    assert f(H, FAKE, 4, 4, None, 0) == INV
+    assert f(H, None, -1, -1, None, 7) == INV              # nnz is looked at first
