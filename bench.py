@@ -275,6 +275,25 @@ def dominant_kernels(is_spmm: bool, launches_per_step: float, b_row_bytes: int) 
     return "SpmvShortRowsKernel | SpmvMediumShortKernel"
 
 
+class SpMVOpStep:
+    """The same product through the SpMVOp plan API (compensated row sums), Z aliasing Y; `step` like the
+    sharded operators so that the timing loops do not care."""
+
+    def __init__(self, d_rp, d_ci, d_v, cols, x, y, alg):
+        from ops_sparse_b200 import api
+        self.h = api.Handle()
+        self.A = api.CsrMatrix(d_rp, d_ci, d_v, d_rp.numel() - 1, cols)
+        self.x, self.y = api.DnVec(x), api.DnVec(y)
+        self.plan = api.SpMVOpPlan(self.h, self.A, self.x, self.y, self.y, alg=alg)
+
+    def step(self, alpha, beta, broadcast=False):
+        self.plan.run(self.x, self.y, self.y, alpha, beta)
+
+    def close(self):
+        self.plan.close()
+        self.h.close()
+
+
 def torch_dtype(kind: str):
     import torch
     return {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[kind]
@@ -321,6 +340,11 @@ def gpu_arm(args, synth, oracle):
         dense = dense_h.to(dev) if rank == 0 else torch.zeros_like(dense_h, device=dev)
         out = out_h.to(dev)
         op = mg.ShardedSpmv(d_rp, d_ci, d_v, A.cols, dense, out)
+        if args.api != "spmv":
+            if cfg["val"] != "f32" or world > 1:
+                raise SystemExit("--api spmvop-alg1 / spmvop-alg2: fp32 SpMV configurations (c1, c2), one GPU")
+            op.close()
+            op = SpMVOpStep(d_rp, d_ci, d_v, A.cols, dense, out, 2 if args.api == "spmvop-alg2" else 1)
     result_h = torch.empty_like(out_h).pin_memory()
     bcast = world > 1
 
@@ -447,16 +471,19 @@ def gpu_arm(args, synth, oracle):
                 if (4 + d_v.element_size()) * A.nnz > L2_BYTES else
                 "inputs fit in L2: this configuration is launch-latency bound, bandwidth fractions are not meaningful",
                 "analysis": "aclsparse*Preprocess once, outside the timed region",
+                "api": args.api,
             },
             "effective_gbs": alg_bytes / (ms_per_step * 1e-3) / 1e9,
             "algorithmic_bytes_per_step": alg_bytes,
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
-                "kernel": dominant_kernels(is_spmm, launches / K, n * dense.element_size() if is_spmm else 0),
+                "kernel": ("SpmvOpLongRowsKernel + SpmvOpRowsKernel per length class" if args.api == "spmvop-alg2"
+                           else "SpmvOpRowsKernel" if args.api == "spmvop-alg1"
+                           else dominant_kernels(is_spmm, launches / K, n * dense.element_size() if is_spmm else 0)),
                 "launch_ms_mean": launch_ms_mean,
-                "algorithmic_bytes_per_launch": my_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.config) if world == 1 else None,
-                "note": BOUND_NOTES.get(args.config),
+                "algorithmic_bytes_per_launch": my_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.config) if (world == 1 and args.api == "spmv") else None,
+                "note": BOUND_NOTES.get(args.config) if args.api == "spmv" else None,
             },
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE,
@@ -488,6 +515,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU golden timing leg")
+    ap.add_argument("--api", default="spmv", choices=["spmv", "spmvop-alg1", "spmvop-alg2"],
+                    help="resident-operand legs through aclsparseSpMV (default) or the SpMVOp plan API")
     ap.add_argument("--no-graph", action="store_true", help="end-to-end leg: issue every step's operations one by one")
     ap.add_argument("--e2e-panels", type=int, default=4,
                     help="row panels the end-to-end leg pipelines its host copies over (1 = copy, compute, copy)")

@@ -14,8 +14,8 @@
 // Two ways to pick G:
 //   no plan (ALG1)   one G for the whole matrix, from nnz / rows; nothing is analysed;
 //   plan (ALG2)      the analysis orders the rows by descending length class (class c: lengths that
-//                    need c bits); rows of 1024 entries and more get a CTA each, every other class
-//                    range its own G, longest rows first -- the
+//                    need c bits); rows of 1024 entries and more get a CTA each, rows of 64 and more
+//                    a warp, the rest four lanes, longest rows first -- the
 //                    counterpart of the reference's reorder / bin_edge tables
 //                    (spmv_op_kernel.cpp:425-540), built here by a histogram and a scatter.
 #include <cstdint>
@@ -282,15 +282,9 @@ __global__ void SpmvOpScatterKernel(const void *rowOffsets, long long rows, int3
     }
 }
 
-// Lanes for rows whose length needs `bits` bits: about two to four entries per lane.
-inline int LanesForClass(int bits)
-{
-    if (bits <= 0) return 1;
-    const long long shortest = 1ll << (bits - 1);  // the class holds lengths [2^(bits-1), 2^bits)
-    int g = 1;
-    while (g < 32 && shortest > 2 * g) g <<= 1;
-    return g;
-}
+// Lanes for rows whose length needs `bits` bits.  Two ranges only: a launch per class of short rows cost
+// 15 us each for a few hundred thousand entries (five launches, 81 us on the power-law matrix).
+inline int LanesForClass(int bits) { return bits >= 7 ? 32 : 4; }  // 64 entries and more: a warp per row
 
 template <bool kIs64>
 void LaunchRows(const OpArgs &a, int G, cudaStream_t st)
