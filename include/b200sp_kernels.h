@@ -79,13 +79,19 @@ int b200sp_spmv_launch(const int32_t *row_ptr, const int32_t *col_ind, const voi
                        int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars, int comp_type,
                        int val_type, int out_type, void *plan, const int32_t *plan_info, void *stream);
 
+/* Longest row of A, read back to *max_len (synchronises `stream` once).  scratch4 is any 4 bytes of
+ * device memory.  The analysis of the transposed product: it decides `by_nnz` below. */
+int b200sp_spmv_max_row_length(const int32_t *row_ptr, int64_t rows, void *scratch4, int32_t *max_len, void *stream);
+
 /* y = alpha * A^T * x + beta * y (y has `cols` entries).  First scales y by beta, then
  * scatters alpha * x[i] * a_ij into y[j] with atomic adds.  For 16-bit y an fp32
- * accumulator of `cols` floats in `scratch` is used (scratch_bytes >= 4 * cols). */
+ * accumulator of `cols` floats in `scratch` is used (scratch_bytes >= 4 * cols).
+ * by_nnz = 0: a lane group per row (best when rows are alike); by_nnz = 1: a warp per 256 consecutive
+ * non-zeros, whatever their rows (a row of 16384 entries is then spread over 64 warps). */
 int b200sp_spmv_trans_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *x,
                              void *y, int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars,
                              int comp_type, int val_type, int out_type, void *scratch, size_t scratch_bytes,
-                             void *stream);
+                             int by_nnz, void *stream);
 
 /* Largest rows + nnz that b200sp_spmv_f32_noalloc accepts. */
 #define B200SP_NOALLOC_MAX_ITEMS (1LL << 26)

@@ -150,6 +150,9 @@ b200spScalars ReadScalars(const aclsparseContext *h, const void *alpha, const vo
     return s;
 }
 
+constexpr int32_t kTransPlan = 3;       // ActivePlan::spmvInfo[0] of a transposed-product analysis ([1] = longest row)
+constexpr int32_t kTransLongRow = 2048;  // a lane group walks at most this many entries of one row alone
+
 bool PlanMatches(const ActivePlan &p, const void *buffer, const aclsparseSpMatDescr *A)
 {
     return buffer != nullptr && p.kind == PlanKind::kSpmv && p.buffer == buffer && p.rowPtr == A->offsets &&
@@ -192,7 +195,26 @@ aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, aclsparseOpe
         ValidateSpmv("aclsparseSpMVPreprocess", handle, opA, matA, vecX, vecY, computeType, alg, &c);
     if (st != ACL_SPARSE_STATUS_SUCCESS) return st;
     if (externalBuffer == nullptr) return ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES;
-    if (c.trans) return ACL_SPARSE_STATUS_SUCCESS;  // the scatter path has nothing to analyse
+    if (c.trans) {
+        // The scatter path only wants to know whether some row is far longer than a warp should walk alone.
+        ActivePlan t;
+        int32_t maxLen = 0;
+        const int rcT = b200sp_spmv_max_row_length(static_cast<const int32_t *>(matA->offsets), matA->rows,
+                                                   externalBuffer, &maxLen, handle->stream);
+        if (rcT != 0) {
+            B200SP_LOGE("aclsparseSpMVPreprocess: analysis failed (cuda error %d)", rcT);
+            return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+        }
+        t.buffer = externalBuffer;
+        t.kind = PlanKind::kSpmv;
+        t.rowPtr = matA->offsets;
+        t.rows = matA->rows;
+        t.nnz = matA->nnz;
+        t.spmvInfo[0] = kTransPlan;
+        t.spmvInfo[1] = maxLen;
+        matA->active = t;
+        return ACL_SPARSE_STATUS_SUCCESS;
+    }
     const size_t bytes = b200sp_spmv_plan_bytes(matA->rows, matA->cols, matA->nnz);
     ActivePlan p;
     // Preprocess is the one place that may synchronise: it asks for the binned plan.
@@ -237,13 +259,20 @@ aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOperation_t o
                 return ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES;
             }
         }
+        // A 16-bit y accumulates in the buffer: whatever non-transposed plan was analysed into it is gone.
+        if (scratch == externalBuffer && scratchBytes > 0 && matA->active.buffer == externalBuffer &&
+            matA->active.spmvInfo[0] != kTransPlan)
+            matA->active = ActivePlan{};
+        // Preprocess'ed and a row of kTransLongRow entries or more: cut the scatter by non-zeros.
+        const bool byNnz = PlanMatches(matA->active, externalBuffer, matA) &&
+                           matA->active.spmvInfo[0] == kTransPlan && matA->active.spmvInfo[1] >= kTransLongRow;
         rc = b200sp_spmv_trans_launch(rowPtr, colInd, matA->values, vecX->values, vecY->values, matA->rows,
                                       matA->cols, matA->nnz, &sc, c.compType, c.valType, c.outType, scratch,
-                                      scratchBytes, stream);
+                                      scratchBytes, byNnz ? 1 : 0, stream);
     } else {
         void *plan = nullptr;
         const int32_t *info = nullptr;
-        if (PlanMatches(matA->active, externalBuffer, matA)) {
+        if (PlanMatches(matA->active, externalBuffer, matA) && matA->active.spmvInfo[0] != kTransPlan) {
             plan = externalBuffer;  // analysed by Preprocess: nothing to redo
             info = matA->active.spmvInfo;
         } else {

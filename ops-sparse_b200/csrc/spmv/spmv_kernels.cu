@@ -948,6 +948,81 @@ __global__ void __launch_bounds__(256) SpmvTransScatterKernel(const int32_t *__r
     }
 }
 
+__global__ void SpmvMaxRowLengthKernel(const int32_t *__restrict__ rowPtr, int rows, int32_t *__restrict__ out)
+{
+    int best = 0;
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        const int len = rowPtr[r + 1] - rowPtr[r];
+        best = len > best ? len : best;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const int o = __shfl_xor_sync(0xffffffffu, best, off);
+        best = o > best ? o : best;
+    }
+    if ((threadIdx.x & 31) == 0 && best > 0) atomicMax(out, best);
+}
+
+// The same scatter cut by non-zeros instead of rows: a warp takes kTransChunk consecutive entries,
+// whatever rows they belong to, and every lane finds the row of its entry by a binary search among
+// the rows the chunk touches.  A scatter needs no per-row reduction, so a row of 16384 entries is
+// simply spread over 64 warps; with a lane group per row it is one warp's 512 sequential trips.
+constexpr int kTransChunk = 256;
+template <typename CompT, typename ValT, typename AccT>
+__global__ void __launch_bounds__(256) SpmvTransScatterNnzKernel(const int32_t *__restrict__ rowPtr,
+                                                                  const int32_t *__restrict__ colInd,
+                                                                  const ValT *__restrict__ val,
+                                                                  const ValT *__restrict__ x,
+                                                                  AccT *__restrict__ acc, int rows, int nnz,
+                                                                  Scalars<CompT> sc)
+{
+    const CompT alpha = sc.Alpha();
+    const int lane = threadIdx.x & 31;
+    const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
+    const long long chunks = ((long long)nnz + kTransChunk - 1) / kTransChunk;
+    auto rowOf = [&](int p, int lo, int hi) {  // largest r in [lo, hi] with rowPtr[r] <= p
+        while (lo < hi) {
+            const int mid = lo + ((hi - lo + 1) >> 1);
+            if (__ldg(rowPtr + mid) <= p) lo = mid;
+            else hi = mid - 1;
+        }
+        return lo;
+    };
+    // The same for a p that all lanes share: 32 probes per round instead of one (rowPtr[lo] <= p is given).
+    auto warpRowOf = [&](int p, int lo, int hi) {
+        while (hi > lo) {
+            const long long span = (long long)hi - lo;
+            if (span <= 32) {
+                const int cand = lo + 1 + lane;
+                const bool ok = cand <= hi && __ldg(rowPtr + cand) <= p;
+                lo += __popc(__ballot_sync(0xffffffffu, ok));  // the probes are monotone
+                break;
+            }
+            const int cand = lo + (int)((lane + 1) * span / 32);  // lane 31 probes hi
+            const bool ok = __ldg(rowPtr + cand) <= p;
+            const int k = __popc(__ballot_sync(0xffffffffu, ok));
+            const int newLo = k == 0 ? lo : lo + (int)((long long)k * span / 32);
+            const int newHi = k == 32 ? hi : lo + (int)((long long)(k + 1) * span / 32) - 1;
+            lo = newLo;
+            hi = newHi;
+        }
+        return lo;
+    };
+    for (long long c = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < chunks; c += warpsTotal) {
+        const int c0 = (int)(c * kTransChunk);
+        const int c1 = c0 + kTransChunk < nnz ? c0 + kTransChunk : nnz;
+        const int rFirst = warpRowOf(c0, 0, rows - 1);
+        const int rLast = warpRowOf(c1 - 1, rFirst, rows - 1);
+        for (int p = c0 + lane; p < c1; p += 32) {
+            const int r = rowOf(p, rFirst, rLast);
+            const CompT xv = alpha * Widen<CompT>(__ldg(x + r));
+            if (xv == CompT(0)) continue;
+            atomicAdd(acc + __ldcs(colInd + p), static_cast<AccT>(xv * Widen<CompT>(__ldcs(val + p))));
+        }
+    }
+}
+
 template <typename OutT>
 __global__ void SpmvTransNarrowKernel(const float *__restrict__ acc, OutT *__restrict__ y, int n)
 {
@@ -1209,7 +1284,7 @@ int LaunchTyped(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
 template <typename CompT, typename ValT, typename OutT>
 int LaunchTransTyped(const int32_t *rowPtr, const int32_t *colInd, const void *val, const void *x, void *y,
                      int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *s, void *scratch,
-                     size_t scratchBytes, cudaStream_t stream)
+                     size_t scratchBytes, bool byNnz, cudaStream_t stream)
 {
     const Scalars<CompT> sc = MakeScalars<CompT>(s);
     if (cols == 0) return 0;
@@ -1218,6 +1293,8 @@ int LaunchTransTyped(const int32_t *rowPtr, const int32_t *colInd, const void *v
     const int G = GroupWidthFor(rows, nnz);
     const int64_t want = rows > 0 ? (rows * G + 255) / 256 : 1;
     const unsigned rowBlocks = (unsigned)(want < (int64_t)sms * 32 ? want : sms * 32);
+    const int64_t wantNnz = (nnz + 8 * kTransChunk - 1) / (8 * kTransChunk);  // eight warps, one chunk each
+    const unsigned nnzBlocks = (unsigned)(wantNnz < (int64_t)sms * 32 ? (wantNnz > 0 ? wantNnz : 1) : sms * 32);
     constexpr bool kNarrowOut = sizeof(OutT) == 2;
     if constexpr (kNarrowOut) {
         if (scratch == nullptr || scratchBytes < sizeof(float) * (size_t)cols) return (int)cudaErrorInvalidValue;
@@ -1226,8 +1303,13 @@ int LaunchTransTyped(const int32_t *rowPtr, const int32_t *colInd, const void *v
                                                                                  (int)cols, sc);
         b200sp_note_launches(1);
         if (rows > 0) {
-            SpmvTransScatterKernel<CompT, ValT, float><<<rowBlocks, 256, 0, stream>>>(
-                rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(x), acc, (int)rows, sc, G);
+            if (byNnz && nnz > 0)
+                SpmvTransScatterNnzKernel<CompT, ValT, float><<<nnzBlocks, 256, 0, stream>>>(
+                    rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(x), acc, (int)rows,
+                    (int)nnz, sc);
+            else
+                SpmvTransScatterKernel<CompT, ValT, float><<<rowBlocks, 256, 0, stream>>>(
+                    rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(x), acc, (int)rows, sc, G);
             b200sp_note_launches(1);
         }
         SpmvTransNarrowKernel<OutT><<<eltBlocks, 256, 0, stream>>>(acc, static_cast<OutT *>(y), (int)cols);
@@ -1237,8 +1319,13 @@ int LaunchTransTyped(const int32_t *rowPtr, const int32_t *colInd, const void *v
         SpmvTransScaleKernel<CompT, OutT, OutT><<<eltBlocks, 256, 0, stream>>>(acc, acc, (int)cols, sc);
         b200sp_note_launches(1);
         if (rows > 0) {
-            SpmvTransScatterKernel<CompT, ValT, OutT><<<rowBlocks, 256, 0, stream>>>(
-                rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(x), acc, (int)rows, sc, G);
+            if (byNnz && nnz > 0)
+                SpmvTransScatterNnzKernel<CompT, ValT, OutT><<<nnzBlocks, 256, 0, stream>>>(
+                    rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(x), acc, (int)rows,
+                    (int)nnz, sc);
+            else
+                SpmvTransScatterKernel<CompT, ValT, OutT><<<rowBlocks, 256, 0, stream>>>(
+                    rowPtr, colInd, static_cast<const ValT *>(val), static_cast<const ValT *>(x), acc, (int)rows, sc, G);
             b200sp_note_launches(1);
         }
     }
@@ -1370,15 +1457,33 @@ int b200sp_spmv_launch(const int32_t *row_ptr, const int32_t *col_ind, const voi
     return rc < 0 ? (int)cudaErrorInvalidValue : rc;
 }
 
+int b200sp_spmv_max_row_length(const int32_t *row_ptr, int64_t rows, void *scratch4, int32_t *max_len, void *stream)
+{
+    if (max_len == nullptr || scratch4 == nullptr) return (int)cudaErrorInvalidValue;
+    *max_len = 0;
+    if (rows <= 0) return 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(scratch4, 0, sizeof(int32_t), st);
+    if (e != cudaSuccess) return (int)e;
+    const long long want = (rows + 255) / 256;
+    const long long cap = (long long)b200sp_sm_count() * 16;
+    SpmvMaxRowLengthKernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(row_ptr, (int)rows,
+                                                                             static_cast<int32_t *>(scratch4));
+    b200sp_note_launches(1);
+    e = cudaMemcpyAsync(max_len, scratch4, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaStreamSynchronize(st);
+}
+
 int b200sp_spmv_trans_launch(const int32_t *row_ptr, const int32_t *col_ind, const void *val, const void *x,
                              void *y, int64_t rows, int64_t cols, int64_t nnz, const b200spScalars *scalars,
                              int comp_type, int val_type, int out_type, void *scratch, size_t scratch_bytes,
-                             void *stream)
+                             int by_nnz, void *stream)
 {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int rc = DispatchTypes(comp_type, val_type, out_type, [&]<typename C, typename V, typename O>() {
         return LaunchTransTyped<C, V, O>(row_ptr, col_ind, val, x, y, rows, cols, nnz, scalars, scratch,
-                                         scratch_bytes, st);
+                                         scratch_bytes, by_nnz != 0, st);
     });
     return rc < 0 ? (int)cudaErrorInvalidValue : rc;
 }

@@ -388,3 +388,23 @@ def test_status_codes_on_device(handle, device, pkg):
     assert L.aclsparseSpMV(handle.raw, 0, None, A.raw, x.raw, None, y.raw, S.ACL_FLOAT, 0, None) == 0
     torch.cuda.synchronize()
     assert y.values.tolist() == [1.0, 1.0]
+
+
+@pytest.mark.parametrize("vt,ot", [("f32", "f32"), ("f16", "f32"), ("i32", "i32")])
+def test_transposed_power_law_rows_cut_by_non_zeros(handle, device, oracle, vt, ot):
+    """Preprocess of a transposed product finds a row of 2048+ entries and the scatter is then cut by
+    non-zeros (a warp per 256 entries, rows looked up by search): empty rows, rows that span many chunks,
+    chunks that span many rows."""
+    from ops_sparse_b200 import synth
+    rng = np.random.default_rng(41)
+    M, N = 20000, 9000
+    lengths = synth.zipf_lengths(rng, M, 1.7, 9000, 20.0)
+    lengths[rng.random(M) < 0.2] = 0
+    lengths[[0, M - 1]] = (5000, 0)
+    rp, ci = random_csr(rng, M, N, lengths)
+    val, x, y = draw(rng, oracle, rp[-1], vt), draw(rng, oracle, M, vt), draw(rng, oracle, N, ot)
+    a, b = (3, -2) if ot == "i32" else (0.75, -0.5)
+    for mode in ("plan", "workspace"):
+        got = run_spmv(handle, device, oracle, rp, ci, val, x, y, a, b, vt, ot, trans=True, rows=M, cols=N, mode=mode)
+        check_against_oracle(oracle, rp, ci, val, x, y, a, b, vt, ot, got, trans=True, cols=N,
+                             what=f"transposed power law {vt}/{mode}")
