@@ -62,8 +62,8 @@ size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz);
  *      -- the medium and long rows are listed in `plan`, and the call synchronises `stream` once
  *      to read the counts back.  b200sp_spmv_launch then runs one kernel per non-empty bin,
  *      concurrently: lane groups over all rows for the short ones, a warp per medium row, and for
- *      the long rows either a CTA per row (kind 1) or, when there are at least 64 of them, their
- *      column indices ascend and cols <= 2,097,152 (kind 2), CTAs that each keep a 32,768-column
+ *      the long rows either a CTA per row (kind 1) or, when there are at least 64 of them and at least
+ *      48 per 32,768 columns, their column indices ascend and cols <= 2,097,152 (kind 2), CTAs that each keep a 32,768-column
  *      block of x in shared memory and sum the pieces of all long rows that fall into it.  The
  *      plan of kind 2 depends on col_ind as well as row_ptr.
  * col_ind may be NULL (kind 2 is then never chosen; a tile plan does not read it).

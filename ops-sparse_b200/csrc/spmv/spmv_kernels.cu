@@ -9,7 +9,7 @@
 // entries ("long", ordered by descending length) as {row, start, end}; a product is then two
 // launches over disjoint rows of y, the first forked onto a side stream so that they share
 // the SMs:
-//   SpmvLongBlockKernel     (64 or more long rows, ascending columns, at most 2 M columns)
+//   SpmvLongBlockKernel     (enough long rows -- 48 per block of x --, ascending columns, at most 2 M columns)
 //                           x is cut into blocks of 32768 columns; a CTA keeps one block in
 //                           shared memory and sums the pieces of all long rows that fall into
 //                           it, so the gathers of more than half of the non-zeros of a
@@ -1432,7 +1432,11 @@ int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t 
     e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return (int)e;
     const double avgShort = host.shortRows > 0 ? (double)host.shortNnz / host.shortRows : 0.0;
-    const bool useBlocked = blocked && host.unsorted == 0 && host.longs >= B200SP_SPMV_MIN_LONG_BLOCKED;
+    // Staging x costs every one of the xBlocks x groups CTAs the same whatever the number of long rows:
+    // on shards of the power-law matrix the blocked kernel won with 2155 long rows (51 vs 70 us) and 4299
+    // (95 vs 133 us), lost with 1070 (44 vs 37 us), tied with 517 -- 32 column blocks each time.
+    const int minLong = B200SP_SPMV_MIN_LONG_BLOCKED > 48 * L.xBlocks ? B200SP_SPMV_MIN_LONG_BLOCKED : 48 * L.xBlocks;
+    const bool useBlocked = blocked && host.unsorted == 0 && host.longs >= minLong;
     plan_info[kInfoKind] = useBlocked ? kPlanBinnedBlocked : kPlanBinned;
     plan_info[kInfoMedium] = host.medium;
     plan_info[kInfoLong] = host.longs;

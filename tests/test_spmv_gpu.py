@@ -187,7 +187,7 @@ def test_long_rows_take_the_column_blocked_kernel(handle, device, oracle, pkg, v
     rows of exactly 1023 / 1024 entries and very long ones."""
     rng = np.random.default_rng(21)
     M, N = 3000, 150000
-    lengths, _ = many_long_rows(rng, M, N, 90)
+    lengths, _ = many_long_rows(rng, M, N, 260)  # five column blocks of x: 48 long rows per block at least
     for r, L in zip((0, 7, 500, 501, 1999, 2999), (1024, 1023, 1500, 5000, 20000, 60000)):
         lengths[r] = L
     rp, ci = random_csr(rng, M, N, lengths)
@@ -205,8 +205,8 @@ def test_column_blocked_kernel_at_block_boundaries(handle, device, oracle, pkg, 
     """x of less than one block, exactly one block, one block and one column, two blocks and five columns;
     dense-ish long rows so that every block boundary is hit, beta = 0."""
     rng = np.random.default_rng(N)
-    M = 400
-    lengths, _ = many_long_rows(rng, M, N, 70, lo=1024, hi=9000)
+    M = 500
+    lengths, _ = many_long_rows(rng, M, N, 160, lo=1024, hi=9000)
     lengths[3] = N  # a full row: every column, so the first and last column of every block
     rp, ci = random_csr(rng, M, N, lengths)
     assert plan_kind(pkg, device, rp, ci, N)[0] == 2
@@ -216,9 +216,11 @@ def test_column_blocked_kernel_at_block_boundaries(handle, device, oracle, pkg, 
 
 
 def test_few_long_rows_keep_a_cta_each(handle, device, oracle, pkg):
+    """Fewer than 48 long rows per column block of x (here 4 blocks, 150 rows): staging x would not pay."""
     rng = np.random.default_rng(23)
     M, N = 2000, 100000
     lengths = rng.integers(0, 40, size=M)
+    lengths[rng.choice(M, 150, replace=False)] = rng.integers(1024, 3000, 150)
     lengths[[5, 900, 1500]] = (1024, 4000, 30000)
     rp, ci = random_csr(rng, M, N, lengths)
     assert plan_kind(pkg, device, rp, ci, N)[0] == 1
@@ -232,7 +234,7 @@ def test_unsorted_long_row_turns_the_column_blocks_off(handle, device, oracle, p
     back to a CTA per row, and every row must still be summed right."""
     rng = np.random.default_rng(22)
     M, N = 500, 90000
-    lengths, where = many_long_rows(rng, M, N, 80)
+    lengths, where = many_long_rows(rng, M, N, 160)
     rp, ci = random_csr(rng, M, N, lengths)
     assert plan_kind(pkg, device, rp, ci, N)[0] == 2
     r = int(where[17])
@@ -248,8 +250,8 @@ def test_unsorted_long_row_turns_the_column_blocks_off(handle, device, oracle, p
 def test_matrix_too_wide_for_column_blocks(handle, device, oracle, pkg):
     """More than 64 blocks of 32768 columns: the long rows keep a CTA each."""
     rng = np.random.default_rng(24)
-    M, N = 300, 64 * 32768 + 1
-    lengths, _ = many_long_rows(rng, M, N, 70, lo=1024, hi=3000)
+    M, N = 3200, 64 * 32768 + 1
+    lengths, _ = many_long_rows(rng, M, N, 3100, lo=1024, hi=1100)  # 64 blocks want 3072 long rows
     rp, ci = random_csr(rng, M, N, lengths)
     assert plan_kind(pkg, device, rp, ci, N)[0] == 1
     assert plan_kind(pkg, device, rp, ci, N - 1)[0] == 2
