@@ -99,6 +99,24 @@ typedef enum aclsparseSpMVOpAlg_t {
     ACL_SPARSE_SPMVOP_ALG2
 } aclsparseSpMVOpAlg_t;
 
+/* Legacy matrix descriptor and its enums (reference include/cann_ops_sparse.h:188-210). */
+struct aclsparseMatDescr;
+typedef struct aclsparseMatDescr *aclsparseMatDescr_t;
+typedef enum aclsparseMatrixType_t {
+    ACL_SPARSE_MATRIX_TYPE_GENERAL = 0,
+    ACL_SPARSE_MATRIX_TYPE_SYMMETRIC,
+    ACL_SPARSE_MATRIX_TYPE_HERMITIAN,
+    ACL_SPARSE_MATRIX_TYPE_TRIANGULAR
+} aclsparseMatrixType_t;
+typedef enum aclsparseDiagType_t {
+    ACL_SPARSE_DIAG_TYPE_NON_UNIT = 0,
+    ACL_SPARSE_DIAG_TYPE_UNIT
+} aclsparseDiagType_t;
+typedef enum aclsparseFillMode_t {
+    ACL_SPARSE_FILL_MODE_LOWER = 0,
+    ACL_SPARSE_FILL_MODE_UPPER
+} aclsparseFillMode_t;
+
 /* ---- opaque types (reference :30-47, 72-78) ---- */
 struct aclsparseSpMVOpDescr;
 struct aclsparseSpMVOpPlan;
@@ -286,6 +304,30 @@ aclsparseStatus_t aclsparseSpMVOp(aclsparseHandle_t handle, aclsparseSpMVOpPlan_
  * pipelines that assemble A as triplets. ---- */
 aclsparseStatus_t aclsparseXcoo2csr(aclsparseHandle_t handle, const int *cooRowInd, int nnz, int m, int *csrRowPtr,
                                     aclsparseIndexBase_t idxBase);
+
+/* ---- Legacy matrix descriptor (reference include/cann_ops_sparse.h:906-919,
+ * sparse/common/aclsparse_matdescr.cpp:25-108): setters ignore a NULL descriptor, getters return the
+ * default for one. ---- */
+aclsparseStatus_t aclsparseCreateMatDescr(aclsparseMatDescr_t *descr);
+aclsparseStatus_t aclsparseDestroyMatDescr(aclsparseMatDescr_t descr);
+void aclsparseSetMatType(aclsparseMatDescr_t descr, aclsparseMatrixType_t type);
+void aclsparseSetMatIndexBase(aclsparseMatDescr_t descr, aclsparseIndexBase_t base);
+void aclsparseSetMatDiagType(aclsparseMatDescr_t descr, aclsparseDiagType_t diagType);
+void aclsparseSetMatFillMode(aclsparseMatDescr_t descr, aclsparseFillMode_t fillMode);
+aclsparseMatrixType_t aclsparseGetMatType(aclsparseMatDescr_t descr);
+aclsparseIndexBase_t aclsparseGetMatIndexBase(aclsparseMatDescr_t descr);
+aclsparseDiagType_t aclsparseGetMatDiagType(aclsparseMatDescr_t descr);
+aclsparseFillMode_t aclsparseGetMatFillMode(aclsparseMatDescr_t descr);
+
+/* ---- Stable sort of the column indices inside every CSR row, permutation P carried along (reference
+ * include/cann_ops_sparse.h:1664-1711, sparse/csrsort/arch35/csrsort_host.cpp:146-222).  csrRowPtr,
+ * csrColInd, P and pBuffer are DEVICE pointers; P is permuted like csrColInd (pass the identity to get
+ * the gather indices for the values).  Only descrA's index base is used.  The workspace is larger than
+ * the reference's 8 bytes per entry (the library sort's own storage comes on top). ---- */
+aclsparseStatus_t aclsparseXcsrsort_bufferSizeExt(aclsparseHandle_t handle, int m, int n, int nnz, const int *csrRowPtr,
+                                                  const int *csrColInd, size_t *pBufferSizeInBytes);
+aclsparseStatus_t aclsparseXcsrsort(aclsparseHandle_t handle, int m, int n, int nnz, const aclsparseMatDescr_t descrA,
+                                    const int *csrRowPtr, int *csrColInd, int *P, void *pBuffer);
 
 #ifdef __cplusplus
 }

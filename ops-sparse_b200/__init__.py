@@ -114,6 +114,18 @@ _SIGNATURES = {
     "aclsparseSpMVOp_setGlobalUserData": [P, P, ctypes.c_char_p, P, c_size_t],
     "aclsparseSpMVOp": [P, P, P, P, P, P, P],
     "aclsparseXcoo2csr": [P, P, c_int, c_int, P, c_int],
+    "aclsparseCreateMatDescr": [POINTER(P)],
+    "aclsparseDestroyMatDescr": [P],
+    "aclsparseSetMatType": [P, c_int],
+    "aclsparseSetMatIndexBase": [P, c_int],
+    "aclsparseSetMatDiagType": [P, c_int],
+    "aclsparseSetMatFillMode": [P, c_int],
+    "aclsparseGetMatType": [P],
+    "aclsparseGetMatIndexBase": [P],
+    "aclsparseGetMatDiagType": [P],
+    "aclsparseGetMatFillMode": [P],
+    "aclsparseXcsrsort_bufferSizeExt": [P, c_int, c_int, c_int, P, P, POINTER(c_size_t)],
+    "aclsparseXcsrsort": [P, c_int, c_int, c_int, P, P, P, P, P],
     # multi-GPU helpers (include/b200sp_mg.h)
     "b200spMgPartitionRows": [P, c_int64, c_int32, POINTER(c_int64)],
 }

@@ -29,6 +29,7 @@ SOURCES = [
     "spmv_op/spmv_op_host.cpp",
     "spmv_op/spmv_op_kernels.cu",
     "convert/coo2csr.cu",
+    "convert/csrsort.cu",
     "spmm/spmm_host.cpp",
     "spmm/spmm_kernels.cu",
     "mg/partition.cpp",

@@ -216,3 +216,44 @@ def test_coo2csr_argument_checks_without_device(pkg):
     assert f(H, None, 4, 4, FAKE, 0) == INV
     assert f(H, FAKE, 4, 4, None, 0) == INV
     assert f(H, None, -1, -1, None, 7) == INV              # nnz is looked at first
+
+
+def test_matdescr_and_csrsort_argument_checks_without_device(pkg):
+    """sparse/common/aclsparse_matdescr.cpp:25-108 and sparse/csrsort/arch35/csrsort_host.cpp:52-74, 146-222."""
+    L, S = pkg.lib(), pkg
+    INV = S.ACL_SPARSE_STATUS_INVALID_VALUE
+    D = c_void_p()
+    assert L.aclsparseCreateMatDescr(None) == INV
+    assert L.aclsparseCreateMatDescr(byref(D)) == 0 and D.value
+    assert (L.aclsparseGetMatType(D), L.aclsparseGetMatIndexBase(D), L.aclsparseGetMatDiagType(D),
+            L.aclsparseGetMatFillMode(D)) == (0, 0, 0, 0)
+    L.aclsparseSetMatType(D, 3); L.aclsparseSetMatIndexBase(D, 1); L.aclsparseSetMatDiagType(D, 1)
+    L.aclsparseSetMatFillMode(D, 1)
+    assert (L.aclsparseGetMatType(D), L.aclsparseGetMatIndexBase(D), L.aclsparseGetMatDiagType(D),
+            L.aclsparseGetMatFillMode(D)) == (3, 1, 1, 1)
+    L.aclsparseSetMatIndexBase(None, 1)  # setters ignore NULL, getters answer the default for it
+    assert L.aclsparseGetMatIndexBase(None) == 0 and L.aclsparseGetMatType(None) == 0
+
+    H = c_void_p(0x10)
+    size = c_size_t(99)
+    q = L.aclsparseXcsrsort_bufferSizeExt
+    assert q(None, 4, 4, 4, FAKE, FAKE, byref(size)) == S.ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR
+    assert q(H, 4, 4, 4, FAKE, FAKE, None) == INV
+    assert q(H, -1, 4, 4, FAKE, FAKE, byref(size)) == INV
+    assert q(H, 0, 4, 4, FAKE, FAKE, byref(size)) == INV      # entries but no rows
+    assert q(H, 4, 0, 4, FAKE, FAKE, byref(size)) == INV      # entries but no columns
+    assert q(H, 4, 4, 4, None, FAKE, byref(size)) == INV
+    assert q(H, 4, 4, 4, FAKE, None, byref(size)) == INV
+    assert q(H, 4, 4, 0, FAKE, None, byref(size)) == 0 and size.value == 0
+
+    f = L.aclsparseXcsrsort
+    assert f(None, 4, 4, 4, D, FAKE, FAKE, FAKE, FAKE) == S.ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR
+    assert f(H, 4, 4, -4, D, FAKE, FAKE, FAKE, FAKE) == INV
+    assert f(H, 4, 4, 4, None, FAKE, FAKE, FAKE, FAKE) == INV
+    L.aclsparseSetMatIndexBase(D, 5)
+    assert f(H, 4, 4, 4, D, FAKE, FAKE, FAKE, FAKE) == INV
+    L.aclsparseSetMatIndexBase(D, 0)
+    assert f(H, 4, 4, 0, D, FAKE, None, None, None) == 0          # nothing to sort
+    assert f(H, 4, 4, 4, D, FAKE, FAKE, None, FAKE) == INV
+    assert f(H, 4, 4, 4, D, FAKE, FAKE, FAKE, None) == INV
+    assert L.aclsparseDestroyMatDescr(D) == 0 and L.aclsparseDestroyMatDescr(None) == 0

@@ -64,3 +64,108 @@ def test_coo2csr_feeds_spmv(pkg, handle, device, oracle):
     import helpers
     helpers.assert_rowwise(dy.values.cpu().numpy().astype(np.float64), gold.astype(np.float64), scale,
                            helpers.TOL["f32"], "coo2csr -> spmv")
+
+
+def stable_row_sort(rp, ci, base):
+    """Per row: stable argsort of the column indices (what the reference documents for P)."""
+    out_ci, perm = ci.copy(), np.arange(ci.size, dtype=np.int32)
+    for r in range(rp.size - 1):
+        s, e = rp[r] - base, rp[r + 1] - base
+        order = np.argsort(ci[s:e], kind="stable")
+        out_ci[s:e] = ci[s:e][order]
+        perm[s:e] = (s + order).astype(np.int32)
+    return out_ci, perm
+
+
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("m,n,mean_len,dups", [(1, 1, 1, False), (50, 40, 12, True), (3000, 5000, 30, False),
+                                                (200, 100000, 3000, False), (20000, 300, 4, True), (64, 64, 0, False)])
+def test_csrsort(pkg, handle, device, m, n, mean_len, dups, base):
+    from ctypes import byref, c_size_t, c_void_p
+    L = pkg.lib()
+    rng = np.random.default_rng(m + 7 * n + base)
+    lengths = rng.poisson(mean_len, size=m).astype(np.int64) if mean_len else np.zeros(m, np.int64)
+    if not dups:
+        lengths = np.minimum(lengths, n)
+    rp = np.zeros(m + 1, np.int32)
+    rp[1:] = np.cumsum(lengths)
+    nnz = int(rp[-1])
+    cols = [rng.integers(0, n, size=int(k)) if dups else rng.permutation(n)[:int(k)] for k in lengths]
+    ci = (np.concatenate(cols) if nnz else np.zeros(0)).astype(np.int32) + base
+    rp = rp + base
+    want_ci, want_p = stable_row_sort(rp, ci, base)
+
+    d_rp, d_ci = torch.from_numpy(rp).to(device), torch.from_numpy(ci).to(device)
+    d_p = torch.arange(nnz, dtype=torch.int32, device=device)
+    descr = c_void_p()
+    assert L.aclsparseCreateMatDescr(byref(descr)) == 0
+    L.aclsparseSetMatIndexBase(descr, base)
+    size = c_size_t()
+    ptr = lambda t: c_void_p(t.data_ptr()) if t.numel() else None
+    assert L.aclsparseXcsrsort_bufferSizeExt(handle.raw, m, n, nnz, ptr(d_rp), ptr(d_ci), byref(size)) == 0
+    assert (size.value >= 8 * nnz) if nnz else size.value == 0
+    buf = torch.empty(max(size.value, 1), dtype=torch.uint8, device=device)
+    assert L.aclsparseXcsrsort(handle.raw, m, n, nnz, descr, ptr(d_rp), ptr(d_ci), ptr(d_p), ptr(buf)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(d_ci.cpu().numpy(), want_ci)
+    assert np.array_equal(d_p.cpu().numpy(), want_p)     # stable: equal columns keep their order
+    assert np.array_equal(d_rp.cpu().numpy(), rp)        # untouched
+    assert L.aclsparseDestroyMatDescr(descr) == 0
+
+
+def test_csrsort_lets_the_blocked_long_row_kernel_in(pkg, handle, device, oracle):
+    """Unsorted long rows keep aclsparseSpMV on a CTA per long row; after csrsort (values gathered through P) the
+    analysis cuts them at the column blocks of x, and the product is the same within tolerance."""
+    from ctypes import byref, c_int32, c_int64, c_size_t, c_void_p
+    from ops_sparse_b200 import api, synth
+    import helpers
+    L = pkg.lib()
+    rng = np.random.default_rng(12)
+    M, N = 600, 60000
+    lengths = rng.integers(0, 10, size=M)
+    lengths[rng.choice(M, 200, replace=False)] = rng.integers(1024, 4000, 200)
+    A = synth.csr_from_lengths(rng, lengths, N, synth.normal)
+    ci = A.col_ind.copy()
+    for r in range(M):  # shuffle every row
+        s, e = A.row_ptr[r], A.row_ptr[r + 1]
+        ci[s:e] = rng.permutation(ci[s:e])
+    x, y = rng.standard_normal(N).astype(np.float32), rng.standard_normal(M).astype(np.float32)
+    gold = oracle.spmv(A.row_ptr, ci, A.values, x, y, 1.25, 0.5)
+    scale = 1.25 * oracle.spmv_abs_rowsum(A.row_ptr, ci, A.values, x) + np.abs(0.5 * y)
+
+    L.b200sp_spmv_plan_bytes.restype = c_size_t
+    L.b200sp_spmv_plan_bytes.argtypes = [c_int64, c_int64, c_int64]
+    L.b200sp_spmv_analyze.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]
+    d_rp, d_ci = torch.from_numpy(A.row_ptr).to(device), torch.from_numpy(ci).to(device)
+    d_v = torch.from_numpy(A.values).to(device)
+
+    def kind():
+        nb = L.b200sp_spmv_plan_bytes(M, N, A.nnz)
+        plan = torch.empty(nb, dtype=torch.uint8, device=device)
+        info = (c_int32 * 4)()
+        assert L.b200sp_spmv_analyze(c_void_p(d_rp.data_ptr()), c_void_p(d_ci.data_ptr()), M, N, A.nnz,
+                                     c_void_p(plan.data_ptr()), nb, info, None) == 0
+        return info[0]
+
+    def product(values):
+        Mx = api.CsrMatrix(d_rp, d_ci, values, M, N)
+        dx, dy = api.DnVec(torch.from_numpy(x).to(device)), api.DnVec(torch.from_numpy(y).to(device))
+        buf = api.spmv_preprocess(handle, Mx, dx, dy)
+        api.spmv(handle, Mx, dx, dy, 1.25, 0.5, buffer=buf)
+        torch.cuda.synchronize()
+        return dy.values.cpu().numpy().astype(np.float64)
+
+    assert kind() == 1
+    helpers.assert_rowwise(product(d_v), gold.astype(np.float64), scale, helpers.TOL["f32"], "unsorted")
+    descr, size = c_void_p(), c_size_t()
+    assert L.aclsparseCreateMatDescr(byref(descr)) == 0
+    assert L.aclsparseXcsrsort_bufferSizeExt(handle.raw, M, N, A.nnz, c_void_p(d_rp.data_ptr()),
+                                             c_void_p(d_ci.data_ptr()), byref(size)) == 0
+    buf = torch.empty(size.value, dtype=torch.uint8, device=device)
+    d_p = torch.arange(A.nnz, dtype=torch.int32, device=device)
+    assert L.aclsparseXcsrsort(handle.raw, M, N, A.nnz, descr, c_void_p(d_rp.data_ptr()), c_void_p(d_ci.data_ptr()),
+                               c_void_p(d_p.data_ptr()), c_void_p(buf.data_ptr())) == 0
+    torch.cuda.synchronize()
+    assert kind() == 2
+    helpers.assert_rowwise(product(d_v[d_p.long()]), gold.astype(np.float64), scale, helpers.TOL["f32"], "sorted")
+    L.aclsparseDestroyMatDescr(descr)
