@@ -117,6 +117,16 @@ typedef enum aclsparseFillMode_t {
     ACL_SPARSE_FILL_MODE_UPPER
 } aclsparseFillMode_t;
 
+/* CSR -> CSC conversion (reference include/cann_ops_sparse.h:1369-1379). */
+typedef enum aclsparseAction_t {
+    ACL_SPARSE_ACTION_SYMBOLIC = 0, /* structure only (colPtr, rowInd) */
+    ACL_SPARSE_ACTION_NUMERIC       /* structure and values */
+} aclsparseAction_t;
+typedef enum aclsparseCsr2CscAlg_t {
+    ACL_SPARSE_CSR2CSC_ALG_DEFAULT = 0,
+    ACL_SPARSE_CSR2CSC_ALG1
+} aclsparseCsr2CscAlg_t;
+
 /* ---- opaque types (reference :30-47, 72-78) ---- */
 struct aclsparseSpMVOpDescr;
 struct aclsparseSpMVOpPlan;
@@ -328,6 +338,21 @@ aclsparseStatus_t aclsparseXcsrsort_bufferSizeExt(aclsparseHandle_t handle, int 
                                                   const int *csrColInd, size_t *pBufferSizeInBytes);
 aclsparseStatus_t aclsparseXcsrsort(aclsparseHandle_t handle, int m, int n, int nnz, const aclsparseMatDescr_t descrA,
                                     const int *csrRowPtr, int *csrColInd, int *P, void *pBuffer);
+
+/* ---- CSR -> CSC (reference include/cann_ops_sparse.h:1366-1440,
+ * sparse/csr2csc_ex2/arch35/csr2csc_ex2_host.cpp:106-232, 539-640).  m x n matrix; all array arguments are
+ * DEVICE pointers; values are int8, fp16, bf16 or fp32 (copied as bytes); entries of one column keep their
+ * row order; with SYMBOLIC, cscVal is not written.  bufferSize ignores its array arguments.  The workspace is
+ * 12 bytes per entry plus the library sort's own storage (the reference needs a few offsets arrays). ---- */
+aclsparseStatus_t aclsparseCsr2cscEx2_bufferSize(aclsparseHandle_t handle, int m, int n, int nnz, const void *csrVal,
+                                                 const int *csrRowPtr, const int *csrColInd, void *cscVal,
+                                                 int *cscColPtr, int *cscRowInd, aclDataType valType,
+                                                 aclsparseAction_t copyValues, aclsparseIndexBase_t idxBase,
+                                                 aclsparseCsr2CscAlg_t alg, size_t *bufferSize);
+aclsparseStatus_t aclsparseCsr2cscEx2(aclsparseHandle_t handle, int m, int n, int nnz, const void *csrVal,
+                                      const int *csrRowPtr, const int *csrColInd, void *cscVal, int *cscColPtr,
+                                      int *cscRowInd, aclDataType valType, aclsparseAction_t copyValues,
+                                      aclsparseIndexBase_t idxBase, aclsparseCsr2CscAlg_t alg, void *buffer);
 
 #ifdef __cplusplus
 }

@@ -114,6 +114,9 @@ _SIGNATURES = {
     "aclsparseSpMVOp_setGlobalUserData": [P, P, ctypes.c_char_p, P, c_size_t],
     "aclsparseSpMVOp": [P, P, P, P, P, P, P],
     "aclsparseXcoo2csr": [P, P, c_int, c_int, P, c_int],
+    "aclsparseCsr2cscEx2_bufferSize": [P, c_int, c_int, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
+                                       POINTER(c_size_t)],
+    "aclsparseCsr2cscEx2": [P, c_int, c_int, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int, P],
     "aclsparseCreateMatDescr": [POINTER(P)],
     "aclsparseDestroyMatDescr": [P],
     "aclsparseSetMatType": [P, c_int],

@@ -30,6 +30,7 @@ SOURCES = [
     "spmv_op/spmv_op_kernels.cu",
     "convert/coo2csr.cu",
     "convert/csrsort.cu",
+    "convert/csr2csc.cu",
     "spmm/spmm_host.cpp",
     "spmm/spmm_kernels.cu",
     "mg/partition.cpp",

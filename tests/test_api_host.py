@@ -257,3 +257,33 @@ def test_matdescr_and_csrsort_argument_checks_without_device(pkg):
     assert f(H, 4, 4, 4, D, FAKE, FAKE, None, FAKE) == INV
     assert f(H, 4, 4, 4, D, FAKE, FAKE, FAKE, None) == INV
     assert L.aclsparseDestroyMatDescr(D) == 0 and L.aclsparseDestroyMatDescr(None) == 0
+
+
+def test_csr2csc_argument_checks_without_device(pkg):
+    """Order and codes of sparse/csr2csc_ex2/arch35/csr2csc_ex2_host.cpp:106-232, 539-640."""
+    L, S = pkg.lib(), pkg
+    H = c_void_p(0x10)
+    INV, NS = S.ACL_SPARSE_STATUS_INVALID_VALUE, S.ACL_SPARSE_STATUS_NOT_SUPPORTED
+    size = c_size_t(5)
+    q, f = L.aclsparseCsr2cscEx2_bufferSize, L.aclsparseCsr2cscEx2
+    F = S.ACL_FLOAT
+    assert q(None, 3, 3, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 0, 0, byref(size)) == S.ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR
+    assert q(H, -1, 3, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 0, 0, byref(size)) == INV
+    assert q(H, 3, -1, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 0, 0, byref(size)) == INV
+    assert q(H, 3, 2 ** 31 - 1, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 0, 0, byref(size)) == INV
+    assert q(H, 3, 3, -1, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 0, 0, byref(size)) == INV
+    assert q(H, 3, 3, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, S.ACL_INT32, 1, 0, 0, byref(size)) == NS   # value type
+    assert q(H, 3, 3, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 2, 0, 0, byref(size)) == INV            # action
+    assert q(H, 3, 3, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 2, 0, byref(size)) == INV            # index base
+    assert q(H, 3, 3, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 0, 2, byref(size)) == INV            # algorithm
+    assert q(H, 3, 3, 3, FAKE, FAKE, FAKE, FAKE, FAKE, FAKE, F, 1, 0, 0, None) == INV
+    for m, n, nnz in ((0, 3, 0), (3, 0, 0), (3, 3, 0)):
+        assert q(H, m, n, nnz, None, None, None, None, None, None, S.ACL_BF16, 0, 1, 1, byref(size)) == 0
+        assert size.value == 0
+    args = lambda **kw: [kw.get(k, d) for k, d in (("csrVal", FAKE), ("rp", FAKE), ("ci", FAKE), ("cscVal", FAKE),
+                                                    ("cp", FAKE), ("ri", FAKE))]
+    call = lambda m=3, n=3, nnz=3, action=1, **kw: f(H, m, n, nnz, *args(**kw), F, action, 0, 0, FAKE)
+    assert call(rp=None) == INV and call(ci=None) == INV and call(csrVal=None) == INV
+    assert call(cp=None) == INV and call(ri=None) == INV and call(cscVal=None) == INV
+    assert call(csrVal=None, cscVal=None, action=0, rp=None) == INV      # SYMBOLIC needs no values, still needs offsets
+    assert call(m=0) == INV and call(n=0) == INV                          # entries without rows / columns

@@ -169,3 +169,94 @@ def test_csrsort_lets_the_blocked_long_row_kernel_in(pkg, handle, device, oracle
     assert kind() == 2
     helpers.assert_rowwise(product(d_v[d_p.long()]), gold.astype(np.float64), scale, helpers.TOL["f32"], "sorted")
     L.aclsparseDestroyMatDescr(descr)
+
+
+@pytest.mark.parametrize("vt", ["f32", "f16", "bf16", "i8"])
+@pytest.mark.parametrize("base,numeric", [(0, True), (1, True), (0, False)])
+def test_csr2csc(pkg, handle, device, oracle, vt, base, numeric):
+    """Against a stable sort of the entries by column (entries of a column keep their row order), bit for bit."""
+    from ctypes import byref, c_size_t, c_void_p
+    from ops_sparse_b200 import synth
+    L, S = pkg.lib(), pkg
+    rng = np.random.default_rng(5 + base)
+    m, n = 4000, 2500
+    lengths = synth.zipf_lengths(rng, m, 1.7, 2000, 9.0)
+    lengths[rng.random(m) < 0.1] = 0
+    A = synth.csr_from_lengths(rng, lengths, n, synth.normal)
+    nnz = A.nnz
+    if vt == "i8":
+        val, acl = rng.integers(-100, 100, nnz).astype(np.int8), S.ACL_INT8
+    elif vt == "f32":
+        val, acl = A.values.astype(np.float32), S.ACL_FLOAT
+    else:
+        val, acl = oracle.to_storage(A.values.astype(np.float32), vt), (S.ACL_FLOAT16 if vt == "f16" else S.ACL_BF16)
+    perm = np.argsort(A.col_ind, kind="stable")
+    row_of = np.repeat(np.arange(m, dtype=np.int32), np.diff(A.row_ptr))
+    want_ri = row_of[perm] + base
+    want_val = val[perm]
+    want_cp = np.zeros(n + 1, np.int64)
+    want_cp[1:] = np.cumsum(np.bincount(A.col_ind, minlength=n))
+    want_cp = (want_cp + base).astype(np.int32)
+
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    d_rp, d_ci, d_v = dev(A.row_ptr + base), dev(A.col_ind + base), dev(val.view(np.uint8).reshape(nnz, -1))
+    o_v = torch.full_like(d_v, 0x5A)
+    o_cp = torch.full((n + 1,), -3, dtype=torch.int32, device=device)
+    o_ri = torch.full((nnz,), -3, dtype=torch.int32, device=device)
+    P = lambda t: c_void_p(t.data_ptr())
+    size = c_size_t()
+    action = 1 if numeric else 0
+    assert L.aclsparseCsr2cscEx2_bufferSize(handle.raw, m, n, nnz, None, None, None, None, None, None, acl, action, base,
+                                            0, byref(size)) == 0 and size.value >= 12 * nnz
+    buf = torch.empty(size.value, dtype=torch.uint8, device=device)
+    assert L.aclsparseCsr2cscEx2(handle.raw, m, n, nnz, P(d_v), P(d_rp), P(d_ci), P(o_v), P(o_cp), P(o_ri), acl, action,
+                                 base, 0, P(buf)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(o_cp.cpu().numpy(), want_cp)
+    assert np.array_equal(o_ri.cpu().numpy(), want_ri)
+    got_v = o_v.cpu().numpy()
+    if numeric:
+        assert np.array_equal(got_v, want_val.view(np.uint8).reshape(nnz, -1))
+    else:
+        assert np.all(got_v == 0x5A)  # SYMBOLIC leaves cscVal alone
+
+
+def test_csr2csc_empty_matrix_and_transposed_product(pkg, handle, device, oracle):
+    """nnz = 0 fills the column offsets with the base; the CSC arrays of A, read as the CSR arrays of A^T, give
+    y = A^T x through the non-transposed (atomic-free) product."""
+    from ctypes import byref, c_size_t, c_void_p
+    from ops_sparse_b200 import api, synth
+    import helpers
+    L, S = pkg.lib(), pkg
+    P = lambda t: c_void_p(t.data_ptr())
+    cp = torch.full((8,), -1, dtype=torch.int32, device=device)
+    assert L.aclsparseCsr2cscEx2(handle.raw, 5, 7, 0, None, P(cp), None, None, P(cp), None, S.ACL_FLOAT, 1, 1, 0,
+                                 None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(cp.cpu().numpy(), np.ones(8, np.int32))
+
+    rng = np.random.default_rng(8)
+    m, n = 3000, 2000
+    A = synth.csr_from_lengths(rng, synth.zipf_lengths(rng, m, 1.8, 1500, 10.0), n, synth.normal)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    d_rp, d_ci, d_v = dev(A.row_ptr), dev(A.col_ind), dev(A.values)
+    t_rp = torch.empty(n + 1, dtype=torch.int32, device=device)
+    t_ci = torch.empty(A.nnz, dtype=torch.int32, device=device)
+    t_v = torch.empty(A.nnz, dtype=torch.float32, device=device)
+    size = c_size_t()
+    assert L.aclsparseCsr2cscEx2_bufferSize(handle.raw, m, n, A.nnz, None, None, None, None, None, None, S.ACL_FLOAT, 1, 0,
+                                            0, byref(size)) == 0
+    buf = torch.empty(size.value, dtype=torch.uint8, device=device)
+    assert L.aclsparseCsr2cscEx2(handle.raw, m, n, A.nnz, P(d_v), P(d_rp), P(d_ci), P(t_v), P(t_rp), P(t_ci), S.ACL_FLOAT,
+                                 1, 0, 0, P(buf)) == 0
+    x, y = rng.standard_normal(m).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    At = api.CsrMatrix(t_rp, t_ci, t_v, n, m)
+    dx, dy = api.DnVec(dev(x)), api.DnVec(dev(y))
+    pbuf = api.spmv_preprocess(handle, At, dx, dy)
+    api.spmv(handle, At, dx, dy, 1.5, 0.5, buffer=pbuf)
+    torch.cuda.synchronize()
+    gold = oracle.spmv_typed(A.row_ptr, A.col_ind, A.values, x, y, 1.5, 0.5, "f32", "f32", "f32", trans=True, cols=n)
+    prod = np.abs(A.values.astype(np.float64) * np.repeat(x.astype(np.float64), np.diff(A.row_ptr)))
+    scale = 1.5 * np.bincount(A.col_ind, weights=prod, minlength=n)[:n] + np.abs(0.5 * y)
+    helpers.assert_rowwise(dy.values.cpu().numpy().astype(np.float64), gold.astype(np.float64), scale,
+                           helpers.TOL["f32"], "A^T x through csr2csc")
