@@ -127,6 +127,11 @@ typedef enum aclsparseCsr2CscAlg_t {
     ACL_SPARSE_CSR2CSC_ALG1
 } aclsparseCsr2CscAlg_t;
 
+/* SDDMM algorithms (reference include/cann_ops_sparse.h:712-715). */
+typedef enum aclsparseSDDMMAlg_t {
+    ACL_SPARSE_SDDMM_ALG_DEFAULT = 0
+} aclsparseSDDMMAlg_t;
+
 /* ---- opaque types (reference :30-47, 72-78) ---- */
 struct aclsparseSpMVOpDescr;
 struct aclsparseSpMVOpPlan;
@@ -353,6 +358,24 @@ aclsparseStatus_t aclsparseCsr2cscEx2(aclsparseHandle_t handle, int m, int n, in
                                       const int *csrRowPtr, const int *csrColInd, void *cscVal, int *cscColPtr,
                                       int *cscRowInd, aclDataType valType, aclsparseAction_t copyValues,
                                       aclsparseIndexBase_t idxBase, aclsparseCsr2CscAlg_t alg, void *buffer);
+
+/* ---- SDDMM: C = (alpha * op(X) * op(Y) + beta * C) on the pattern of C, values of C updated in place
+ * (reference include/cann_ops_sparse.h:706-745, sparse/sddmm/arch35/sddmm_host.cpp:145-320, 478-764).  op(X) is
+ * m x k, op(Y) is k x n, C is m x n CSR with int32 zero-based indices; (X, Y, C, compute) all fp32 or all fp16
+ * (fp32 accumulation, result saturated to +-65504 before rounding); alpha / beta have the compute type.  The
+ * buffer must not be NULL; nothing is kept in it. ---- */
+aclsparseStatus_t aclsparseSDDMMBufferSize(aclsparseHandle_t handle, aclsparseOperation_t opX, aclsparseOperation_t opY,
+                                           const void *alpha, aclsparseConstDnMatDescr_t matX,
+                                           aclsparseConstDnMatDescr_t matY, const void *beta, aclsparseSpMatDescr_t matC,
+                                           aclDataType computeType, aclsparseSDDMMAlg_t alg, size_t *size);
+aclsparseStatus_t aclsparseSDDMMPreprocess(aclsparseHandle_t handle, aclsparseOperation_t opX, aclsparseOperation_t opY,
+                                           const void *alpha, aclsparseConstDnMatDescr_t matX,
+                                           aclsparseConstDnMatDescr_t matY, const void *beta, aclsparseSpMatDescr_t matC,
+                                           aclDataType computeType, aclsparseSDDMMAlg_t alg, void *buffer);
+aclsparseStatus_t aclsparseSDDMM(aclsparseHandle_t handle, aclsparseOperation_t opX, aclsparseOperation_t opY,
+                                 const void *alpha, aclsparseConstDnMatDescr_t matX, aclsparseConstDnMatDescr_t matY,
+                                 const void *beta, aclsparseSpMatDescr_t matC, aclDataType computeType,
+                                 aclsparseSDDMMAlg_t alg, void *buffer);
 
 #ifdef __cplusplus
 }

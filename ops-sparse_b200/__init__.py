@@ -113,6 +113,10 @@ _SIGNATURES = {
     "aclsparseSpMVOp_destroyPlan": [P],
     "aclsparseSpMVOp_setGlobalUserData": [P, P, ctypes.c_char_p, P, c_size_t],
     "aclsparseSpMVOp": [P, P, P, P, P, P, P],
+    # SDDMM: handle, opX, opY, alpha, matX, matY, beta, matC, computeType, alg, (size* | buffer)
+    "aclsparseSDDMMBufferSize": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, POINTER(c_size_t)],
+    "aclsparseSDDMMPreprocess": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P],
+    "aclsparseSDDMM": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P],
     "aclsparseXcoo2csr": [P, P, c_int, c_int, P, c_int],
     "aclsparseCsr2cscEx2_bufferSize": [P, c_int, c_int, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
                                        POINTER(c_size_t)],

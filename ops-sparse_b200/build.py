@@ -31,6 +31,7 @@ SOURCES = [
     "convert/coo2csr.cu",
     "convert/csrsort.cu",
     "convert/csr2csc.cu",
+    "sddmm/sddmm.cu",
     "spmm/spmm_host.cpp",
     "spmm/spmm_kernels.cu",
     "mg/partition.cpp",
