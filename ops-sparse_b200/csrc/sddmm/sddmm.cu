@@ -69,6 +69,80 @@ __global__ void __launch_bounds__(256) SddmmKernel(const int32_t *__restrict__ r
     }
 }
 
+// 16 bytes of both operands per lane and step: 4 fp32 or 8 fp16 products.
+__device__ __forceinline__ float Dot16(const uint4 &x, const uint4 &y, float acc, float)
+{
+    acc = fmaf(__uint_as_float(x.x), __uint_as_float(y.x), acc);
+    acc = fmaf(__uint_as_float(x.y), __uint_as_float(y.y), acc);
+    acc = fmaf(__uint_as_float(x.z), __uint_as_float(y.z), acc);
+    return fmaf(__uint_as_float(x.w), __uint_as_float(y.w), acc);
+}
+__device__ __forceinline__ float Dot16(const uint4 &x, const uint4 &y, float acc, __half)
+{
+    const __half2 *hx = reinterpret_cast<const __half2 *>(&x);
+    const __half2 *hy = reinterpret_cast<const __half2 *>(&y);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 a = __half22float2(hx[i]), b = __half22float2(hy[i]);
+        acc = fmaf(a.x, b.x, acc);
+        acc = fmaf(a.y, b.y, acc);
+    }
+    return acc;
+}
+
+// The same product when k runs along the contiguous direction of both operands and rows are 16-byte
+// aligned: 128-bit loads.  The first 16-byte piece of the X row of every lane stays in registers while
+// consecutive entries of C share their row (rows of up to 32 pieces -- 128 fp32 or 256 fp16 -- are then
+// read once per row and chunk).
+template <typename T>
+__global__ void __launch_bounds__(256) SddmmVecKernel(const int32_t *__restrict__ rowPtr, const int32_t *__restrict__ colInd,
+                                                      T *__restrict__ cVal, const T *__restrict__ X,
+                                                      const T *__restrict__ Y, int m, int pieces, long long nnz,
+                                                      long long xRow16, long long yRow16, float alpha, float beta,
+                                                      const T *alphaDev, const T *betaDev)
+{
+    const float a = alphaDev ? Load<T>(alphaDev) : alpha;
+    const float b = betaDev ? Load<T>(betaDev) : beta;
+    const int lane = threadIdx.x & 31;
+    const uint4 *X16 = reinterpret_cast<const uint4 *>(X);
+    const uint4 *Y16 = reinterpret_cast<const uint4 *>(Y);
+    const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
+    const long long chunks = (nnz + 31) / 32;
+    for (long long c = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < chunks; c += warpsTotal) {
+        const long long p0 = c * 32;
+        const long long p1 = p0 + 32 < nnz ? p0 + 32 : nnz;
+        int lo = 0, hi = m - 1;
+        while (lo < hi) {
+            const int mid = lo + ((hi - lo + 1) >> 1);
+            if ((long long)__ldg(rowPtr + mid) <= p0) lo = mid;
+            else hi = mid - 1;
+        }
+        int r = lo, cachedRow = -1;
+        uint4 x0 = make_uint4(0, 0, 0, 0);
+        const int myCol = p0 + lane < p1 ? __ldg(colInd + p0 + lane) : 0;  // the chunk's columns, one per lane
+        for (long long p = p0; p < p1; ++p) {
+            while ((long long)__ldg(rowPtr + r + 1) <= p) ++r;
+            const int j = __shfl_sync(0xffffffffu, myCol, (int)(p - p0));
+            const uint4 *xr = X16 + (long long)r * xRow16;
+            const uint4 *yc = Y16 + (long long)j * yRow16;
+            if (r != cachedRow) {
+                if (lane < pieces) x0 = __ldg(xr + lane);
+                cachedRow = r;
+            }
+            float acc = 0.0f;
+            if (lane < pieces) acc = Dot16(x0, __ldg(yc + lane), acc, T());
+            for (int q = lane + 32; q < pieces; q += 32) acc = Dot16(__ldg(xr + q), __ldg(yc + q), acc, T());
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (lane == 0) {
+                float z = a * acc;
+                if (b != 0.0f) z += b * Load<T>(cVal + p);
+                cVal[p] = Store<T>(z);
+            }
+        }
+    }
+}
+
 float HalfBitsToFloat(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
 float ReadScalar(const void *p, aclDataType computeType)  // sddmm_host.cpp:128-139
@@ -144,7 +218,22 @@ int Launch(const aclsparseSpMatDescr *C, const aclsparseDnMatDescr *X, const acl
     const long long chunks = (C->nnz + 31) / 32;
     const long long want = (chunks + 7) / 8;
     const long long cap = (long long)b200sp_sm_count() * 32;
-    SddmmKernel<T><<<(unsigned)(want < cap ? want : cap), 256, 0, stream>>>(
+    const unsigned grid = (unsigned)(want < cap ? want : cap);
+    const long long rowBytes = (long long)k * (long long)sizeof(T);
+    const bool vec = st.xk == 1 && st.yk == 1 && rowBytes % 16 == 0 && (st.xi * (long long)sizeof(T)) % 16 == 0 &&
+                     (st.yj * (long long)sizeof(T)) % 16 == 0 && reinterpret_cast<uintptr_t>(X->values) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(Y->values) % 16 == 0;
+    if (vec) {
+        SddmmVecKernel<T><<<grid, 256, 0, stream>>>(
+            static_cast<const int32_t *>(C->offsets), static_cast<const int32_t *>(C->indices),
+            static_cast<T *>(C->values), static_cast<const T *>(X->values), static_cast<const T *>(Y->values),
+            (int)C->rows, (int)(rowBytes / 16), (long long)C->nnz, st.xi * (long long)sizeof(T) / 16,
+            st.yj * (long long)sizeof(T) / 16, alpha, beta, static_cast<const T *>(alphaDev),
+            static_cast<const T *>(betaDev));
+        b200sp_note_launches(1);
+        return (int)cudaGetLastError();
+    }
+    SddmmKernel<T><<<grid, 256, 0, stream>>>(
         static_cast<const int32_t *>(C->offsets), static_cast<const int32_t *>(C->indices), static_cast<T *>(C->values),
         static_cast<const T *>(X->values), static_cast<const T *>(Y->values), (int)C->rows, k, (long long)C->nnz, st,
         alpha, beta, static_cast<const T *>(alphaDev), static_cast<const T *>(betaDev));

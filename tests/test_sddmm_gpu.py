@@ -114,14 +114,14 @@ def test_ops_orders_and_padding(pkg, handle, device, dtype, opx, ox, opy, oy):
     assert np.all(np.abs(got - want) <= tol * scale + slack + 1e-30), np.max(np.abs(got - want) / (tol * scale + slack + 1e-30))
 
 
+@pytest.mark.parametrize("k", [128, 328])  # rows of 16 / 32 / 41 / 82 sixteen-byte pieces: one per lane, or a loop
 @pytest.mark.parametrize("dtype", ["f32", "f16"])
-def test_graph_shape_device_scalars_and_beta_zero(pkg, handle, device, dtype):
+def test_graph_shape_device_scalars_and_beta_zero(pkg, handle, device, dtype, k):
     """The shape of the backward step of a graph layer: X m x k row-major, Y n x k row-major used transposed;
     scalars on the device; beta = 0 must not read C (NaN in C)."""
     from ops_sparse_b200 import synth
     rng = np.random.default_rng(17)
     m = n = 5000
-    k = 128
     A = synth.csr_from_lengths(rng, synth.zipf_lengths(rng, m, 2.0, 4000, 10.0), n, synth.uniform)
     X, xs, ldx = dense_operand(rng, m, k, "row", 0, dtype)
     Yt, ys, ldy = dense_operand(rng, n, k, "row", 0, dtype)
