@@ -287,3 +287,44 @@ def test_csr2csc_argument_checks_without_device(pkg):
     assert call(cp=None) == INV and call(ri=None) == INV and call(cscVal=None) == INV
     assert call(csrVal=None, cscVal=None, action=0, rp=None) == INV      # SYMBOLIC needs no values, still needs offsets
     assert call(m=0) == INV and call(n=0) == INV                          # entries without rows / columns
+
+
+def test_sddmm_argument_checks_without_device(pkg):
+    """Order and codes of sparse/sddmm/arch35/sddmm_host.cpp:194-320, 478-510, 660-692 (failing cases only: they
+    return before the handle is read)."""
+    L, S = pkg.lib(), pkg
+    H = c_void_p(0x10)
+    INV, NS = S.ACL_SPARSE_STATUS_INVALID_VALUE, S.ACL_SPARSE_STATUS_NOT_SUPPORTED
+    X, Y, C, C64, C1, Xh = (c_void_p() for _ in range(6))
+    assert L.aclsparseCreateDnMat(byref(X), 4, 8, 8, FAKE, S.ACL_FLOAT, 0) == 0
+    assert L.aclsparseCreateDnMat(byref(Xh), 4, 8, 8, FAKE, S.ACL_FLOAT16, 0) == 0
+    assert L.aclsparseCreateDnMat(byref(Y), 8, 5, 5, FAKE, S.ACL_FLOAT, 0) == 0
+    mk = lambda d, off, base: L.aclsparseCreateCsr(byref(d), 4, 5, 6, FAKE, FAKE, FAKE, off, 0, base, S.ACL_FLOAT)
+    assert mk(C, 0, 0) == 0 and mk(C64, S.ACL_SPARSE_INDEX_64I, 0) == 0 and mk(C1, 0, 1) == 0
+    N, T = S.ACL_SPARSE_OP_NON_TRANSPOSE, S.ACL_SPARSE_OP_TRANSPOSE
+    size = c_size_t()
+    q, f, pre = L.aclsparseSDDMMBufferSize, L.aclsparseSDDMM, L.aclsparseSDDMMPreprocess
+    F = S.ACL_FLOAT
+    assert q(None, N, N, FAKE, X, Y, FAKE, C, F, 0, byref(size)) == S.ACL_SPARSE_STATUS_HANDLE_IS_NULLPTR
+    assert q(H, N, N, FAKE, X, Y, FAKE, C, F, 0, None) == INV
+    assert q(H, N, N, None, X, Y, FAKE, C, F, 0, byref(size)) == INV
+    assert q(H, N, N, FAKE, X, Y, FAKE, C, F, 0, byref(size)) == 0 and size.value > 0
+    assert q(H, N, N, FAKE, None, Y, FAKE, C, F, 0, byref(size)) == INV
+    assert q(H, N, N, FAKE, X, Y, FAKE, C64, F, 0, byref(size)) == NS          # int64 row offsets
+    assert q(H, N, N, FAKE, X, Y, FAKE, C1, F, 0, byref(size)) == NS           # one-based
+    assert q(H, 2, N, FAKE, X, Y, FAKE, C, F, 0, byref(size)) == NS            # conjugate transpose
+    assert q(H, N, N, FAKE, Xh, Y, FAKE, C, F, 0, byref(size)) == NS           # mixed types
+    assert q(H, N, N, FAKE, X, Y, FAKE, C, S.ACL_FLOAT16, 0, byref(size)) == NS
+    assert q(H, T, N, FAKE, X, Y, FAKE, C, F, 0, byref(size)) == INV           # X^T is 8 x 4: rows do not match C
+    assert q(H, N, T, FAKE, X, Y, FAKE, C, F, 0, byref(size)) == INV           # Y^T is 5 x 8
+    assert q(H, N, N, FAKE, X, Y, FAKE, C, F, 1, byref(size)) == NS            # algorithm
+    # the compute / preprocess calls check the descriptors before the scalars, and the buffer last
+    assert f(H, N, N, None, None, Y, FAKE, C, F, 0, FAKE) == INV
+    assert f(H, N, N, None, X, Y, FAKE, C, F, 0, FAKE) == INV
+    assert f(H, N, N, FAKE, X, Y, FAKE, C, F, 0, None) == INV
+    assert pre(H, N, N, FAKE, X, Y, FAKE, C, F, 0, None) == S.ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES
+    assert pre(H, N, N, FAKE, X, Y, FAKE, C, F, 0, FAKE) == 0
+    for d in (X, Xh, Y):
+        assert L.aclsparseDestroyDnMat(d) == 0
+    for d in (C, C64, C1):
+        assert L.aclsparseDestroySpMat(d) == 0
