@@ -15,7 +15,8 @@
 //                           it, so the gathers of more than half of the non-zeros of a
 //                           power-law matrix never leave the SM.  The last CTA to finish a group
 //                           of rows adds their per-block partial sums in block order.
-//   SpmvLongListKernel      (otherwise) one CTA per listed row, 128-bit loads.
+//   SpmvAllBinsKernel       (otherwise) one grid for all bins: a CTA per listed long row with 128-bit
+//                           loads first, then the medium and short rows as below; no side stream.
 //   SpmvMediumShortKernel   one grid: first a warp per listed medium row, then every row gets
 //                           a group of G = 2 or 4 lanes (rows longer than 32 entries are
 //                           skipped).  SpmvShortRowsKernel alone when no row is medium.
@@ -442,6 +443,9 @@ constexpr int kLongBlockThreads = B200SP_SPMV_LONG_BLOCK_THREADS;
 #ifndef B200SP_SPMV_PIECE_LANES
 #define B200SP_SPMV_PIECE_LANES 8    // lanes that share one (long row, x block) piece
 #endif
+#ifndef B200SP_SPMV_FUSE_LIST
+#define B200SP_SPMV_FUSE_LIST 1      // long rows that keep a CTA each share one grid with the other bins
+#endif
 #ifndef B200SP_SPMV_MIN_LONG_BLOCKED
 #define B200SP_SPMV_MIN_LONG_BLOCKED 64  // fewer long rows than this: not worth staging x
 #endif
@@ -781,7 +785,7 @@ __device__ __forceinline__ void MediumRowsBody(unsigned bid, const int32_t *__re
     }
 }
 
-template <typename CompT, typename ValT, typename OutT, bool kVec>
+template <typename CompT, typename ValT, typename OutT, bool kVec, int kUnrollQ = kLongUnroll>
 __device__ __forceinline__ void LongRowBody(unsigned bid, const int32_t *__restrict__ colInd,
                                             const ValT *__restrict__ val, const ValT *__restrict__ x,
                                             OutT *__restrict__ y, const int4 *__restrict__ list,
@@ -804,11 +808,11 @@ __device__ __forceinline__ void LongRowBody(unsigned bid, const int32_t *__restr
         const int pe = doHead ? ph : pt;
         const int ce = (doHead || doTail) ? colInd[pe] : 0;
         const ValT vE = (doHead || doTail) ? val[pe] : ValT(0);
-        for (int v = vs + tid; v < ve; v += kLongUnroll * 256) {
-            int4 c[kLongUnroll];
-            Quad<ValT> q[kLongUnroll];
+        for (int v = vs + tid; v < ve; v += kUnrollQ * 256) {
+            int4 c[kUnrollQ];
+            Quad<ValT> q[kUnrollQ];
 #pragma unroll
-            for (int u = 0; u < kLongUnroll; ++u) {
+            for (int u = 0; u < kUnrollQ; ++u) {
                 const int vv = v + 256 * u;
                 if (vv < ve) {
                     c[u] = __ldcs(reinterpret_cast<const int4 *>(colInd) + vv);
@@ -820,7 +824,7 @@ __device__ __forceinline__ void LongRowBody(unsigned bid, const int32_t *__restr
                 }
             }
 #pragma unroll
-            for (int u = 0; u < kLongUnroll; ++u) {
+            for (int u = 0; u < kUnrollQ; ++u) {
                 if (v + 256 * u < ve) {
                     sum += Widen<CompT>(q[u].v[0]) * Widen<CompT>(__ldg(x + c[u].x));
                     sum += Widen<CompT>(q[u].v[1]) * Widen<CompT>(__ldg(x + c[u].y));
@@ -881,6 +885,30 @@ __global__ void __launch_bounds__(256) SpmvLongListKernel(const int32_t *__restr
 {
     __shared__ CompT sWarp[8];
     LongRowBody<CompT, ValT, OutT, kVec>(blockIdx.x, colInd, val, x, y, list, sc, sWarp);
+}
+
+// All three bins in one grid, for matrices whose long rows keep a CTA each: blocks [0, nL) take one long
+// row, the next ceil(nM / 8) eight medium rows, the rest sweep the short rows.  Blocks are handed out in
+// index order, so the longest pieces of work start first.  One launch and no fork / join: on a
+// 131,000-row shard the two-stream form spent more time between its kernels than in them.
+template <typename CompT, typename ValT, typename OutT, int G, bool kVec>
+__global__ void __launch_bounds__(256, 6) SpmvAllBinsKernel(const int32_t *__restrict__ rowPtr,
+                                                             const int32_t *__restrict__ colInd,
+                                                             const ValT *__restrict__ val, const ValT *__restrict__ x,
+                                                             OutT *__restrict__ y, const int4 *__restrict__ listM,
+                                                             const int4 *__restrict__ listL, int nM, int nL, int rows,
+                                                             Scalars<CompT> sc)
+{
+    __shared__ CompT sWarp[8];
+    unsigned b = blockIdx.x;
+    if (b < (unsigned)nL) {
+        LongRowBody<CompT, ValT, OutT, kVec, 2>(b, colInd, val, x, y, listL, sc, sWarp);
+        return;
+    }
+    b -= (unsigned)nL;
+    const unsigned mediumBlocks = ((unsigned)nM + 7u) >> 3;
+    if (b < mediumBlocks) MediumRowsBody<CompT, ValT, OutT>(b, colInd, val, x, y, listM, nM, sc);
+    else ShortRowsBody<CompT, ValT, OutT, G>(b - mediumBlocks, rowPtr, colInd, val, x, y, rows, sc);
 }
 
 // ---------------------------------------------------------------- workspace-free kernel
@@ -1168,6 +1196,24 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
     const int nM = info[kInfoMedium], nL = info[kInfoLong], G = info[kInfoGroup];
     const bool vec = (reinterpret_cast<uintptr_t>(colInd) % 16 == 0) &&
                      (reinterpret_cast<uintptr_t>(val) % (4 * sizeof(ValT)) == 0);
+#if B200SP_SPMV_FUSE_LIST
+    if (nL > 0 && !(info[kInfoKind] == kPlanBinnedBlocked && L.xBlocks > 0)) {
+        const unsigned blocks = (unsigned)nL + (unsigned)((nM + 7) / 8) + (unsigned)((rows * G + 255) / 256);
+        auto launch = [&]<int GG>() {
+            if (vec) SpmvAllBinsKernel<CompT, ValT, OutT, GG, true><<<blocks, 256, 0, stream>>>(
+                rowPtr, colInd, val, x, y, listM, listL, nM, nL, (int)rows, sc);
+            else SpmvAllBinsKernel<CompT, ValT, OutT, GG, false><<<blocks, 256, 0, stream>>>(
+                rowPtr, colInd, val, x, y, listM, listL, nM, nL, (int)rows, sc);
+        };
+        switch (G) {
+            case 2: launch.template operator()<2>(); break;
+            case 8: launch.template operator()<8>(); break;
+            default: launch.template operator()<4>(); break;
+        }
+        b200sp_note_launches(1);
+        return (int)cudaGetLastError();
+    }
+#endif
     // The kernels write disjoint rows of y.  The long rows go first, to a side stream forked from
     // and joined back into the caller's stream; medium and short rows follow in one grid.
     SideLanes *lanes = nL > 0 ? GetSideLanes() : nullptr;
