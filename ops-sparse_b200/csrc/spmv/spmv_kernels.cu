@@ -1197,7 +1197,10 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
     const bool vec = (reinterpret_cast<uintptr_t>(colInd) % 16 == 0) &&
                      (reinterpret_cast<uintptr_t>(val) % (4 * sizeof(ValT)) == 0);
 #if B200SP_SPMV_FUSE_LIST
-    if (nL > 0 && !(info[kInfoKind] == kPlanBinnedBlocked && L.xBlocks > 0)) {
+    // Only for small products (up to 4 M entries): there the fork / join costs more than it buys.  Larger ones
+    // keep two kernels on forked streams -- equal in isolation (36.9 us either way on 7.6 M entries), but four
+    // such products pipelined on three streams with their host copies took 329 us fused against 287 us forked.
+    if (nL > 0 && nnz <= (4ll << 20) && !(info[kInfoKind] == kPlanBinnedBlocked && L.xBlocks > 0)) {
         const unsigned blocks = (unsigned)nL + (unsigned)((nM + 7) / 8) + (unsigned)((rows * G + 255) / 256);
         auto launch = [&]<int GG>() {
             if (vec) SpmvAllBinsKernel<CompT, ValT, OutT, GG, true><<<blocks, 256, 0, stream>>>(
