@@ -1116,6 +1116,23 @@ struct SideLaneSet {
     }
 };
 
+// The side stream gets the highest priority the device offers: its grid is the small one that should be
+// resident first, and (B200SP_SPMV_SIDE_PRIORITY = 0 restores the default) a priority of its own keeps it
+// off the hardware queue of the caller's stream.
+#ifndef B200SP_SPMV_SIDE_PRIORITY
+#define B200SP_SPMV_SIDE_PRIORITY 1
+#endif
+cudaError_t CreateSideStream(cudaStream_t *s)
+{
+#if B200SP_SPMV_SIDE_PRIORITY
+    int least = 0, greatest = 0;
+    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess && greatest < least)
+        return cudaStreamCreateWithPriority(s, cudaStreamNonBlocking, greatest);
+    (void)cudaGetLastError();
+#endif
+    return cudaStreamCreateWithFlags(s, cudaStreamNonBlocking);
+}
+
 SideLanes *GetSideLanes()
 {
     static thread_local SideLaneSet set;
@@ -1124,7 +1141,7 @@ SideLanes *GetSideLanes()
     SideLanes &l = set.lanes[dev];
     if (!l.ready) {
         const bool ok = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess &&
-                        cudaStreamCreateWithFlags(&l.stream[0], cudaStreamNonBlocking) == cudaSuccess &&
+                        CreateSideStream(&l.stream[0]) == cudaSuccess &&
                         cudaEventCreateWithFlags(&l.join[0], cudaEventDisableTiming) == cudaSuccess;
         if (!ok) {
             (void)cudaGetLastError();
