@@ -53,19 +53,23 @@ size_t b200sp_spmv_plan_bytes(int64_t rows, int64_t cols, int64_t nnz);
 /* Bytes a tile plan alone needs (what a per-call analysis with plan_info == NULL writes). */
 size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz);
 
+/* Ints of plan_info that b200sp_spmv_analyze writes and b200sp_spmv_launch reads. */
+#define B200SP_SPMV_PLAN_INFO_INTS 8
+
 /* Analysis pass, two kinds:
  *  plan_info == NULL : tile plan.  Splits the merged (row-end, nnz) sequence of the CSR matrix into
  *      equal tiles and writes the tile table plus zeroed arrival counters into `plan`.  Nothing
  *      synchronises.  b200sp_spmv_launch then runs the merge-path tile kernel.
- *  plan_info != NULL : binned plan (4 ints are written to it: kind = 1 or 2, medium rows, long rows,
- *      lane-group width).  Rows are binned by length -- short (<= 32 entries), medium, long (>= 1024)
- *      -- the medium and long rows are listed in `plan`, and the call synchronises `stream` once
- *      to read the counts back.  b200sp_spmv_launch then runs one kernel per non-empty bin,
- *      concurrently: lane groups over all rows for the short ones, a warp per medium row, and for
- *      the long rows either a CTA per row (kind 1) or, when there are at least 64 of them and at least
- *      48 per 32,768 columns, their column indices ascend and cols <= 2,097,152 (kind 2), CTAs that each keep a 32,768-column
- *      block of x in shared memory and sum the pieces of all long rows that fall into it.  The
- *      plan of kind 2 depends on col_ind as well as row_ptr.
+ *  plan_info != NULL : binned plan.  B200SP_SPMV_PLAN_INFO_INTS ints are written to it: [0] kind = 1 or 2,
+ *      [1] medium rows, [2] long rows, [3] lanes per short row, [4] column blocks of x and [5] columns per
+ *      block (kind 2 only), [6] the length from which a row counts as long, [7] 0.  Rows are binned by length
+ *      -- short (<= 32 entries), medium, long -- the medium and long rows are listed in `plan`, and the call
+ *      synchronises `stream` once to read the counts back.  b200sp_spmv_launch then runs one kernel per
+ *      non-empty bin, concurrently: lane groups over all rows for the short ones, a warp per medium row, and for
+ *      the long rows either a CTA per row (kind 1) or, when there are at least 64 of them and at least 48 per
+ *      column block, their column indices ascend and cols <= 2,097,152 (kind 2), CTAs that each keep a block
+ *      of x (up to 32,768 columns) in shared memory and sum the pieces of all long rows that fall into it.
+ *      The plan of kind 2 depends on col_ind as well as row_ptr, and on the SM count of the current device.
  * col_ind may be NULL (kind 2 is then never chosen; a tile plan does not read it).
  * Returns cudaErrorInvalidValue when plan_bytes is too small. */
 int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols, int64_t nnz,

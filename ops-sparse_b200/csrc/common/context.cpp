@@ -2,7 +2,9 @@
 // Behaviour follows sparse/common/aclsparse_auxiliary.cpp:64-198, 253-279 of the reference;
 // device memory comes from the CUDA runtime instead of aclrtMalloc.
 #include <atomic>
+#include <mutex>
 #include <new>
+#include <unordered_map>
 
 #include "internal.h"
 
@@ -15,6 +17,28 @@ int LogLevel()
         return s ? std::atoi(s) : 1;
     }();
     return level;
+}
+
+
+namespace {
+std::mutex gGenerationMutex;
+std::unordered_map<const void *, uint64_t> gGenerations;
+uint64_t gNextGeneration = 0;
+}  // namespace
+
+uint64_t NoteBufferWrite(const void *buffer)
+{
+    if (buffer == nullptr) return 0;
+    std::lock_guard<std::mutex> lock(gGenerationMutex);
+    return gGenerations[buffer] = ++gNextGeneration;
+}
+
+uint64_t BufferGeneration(const void *buffer)
+{
+    if (buffer == nullptr) return 0;
+    std::lock_guard<std::mutex> lock(gGenerationMutex);
+    const auto it = gGenerations.find(buffer);
+    return it == gGenerations.end() ? 0 : it->second;
 }
 
 }  // namespace b200sp

@@ -57,8 +57,16 @@ struct ActivePlan {
     int64_t nnz = 0;
     int64_t n = 0;         // SpMM only: dense column count the partial-sum area was sized for
     int32_t segments = 0;  // SpMM only: long-row segments found by the analysis
-    int32_t spmvInfo[4] = {0, 0, 0, 0};  // SpMV only: plan_info written by b200sp_spmv_analyze
+    int32_t spmvInfo[B200SP_SPMV_PLAN_INFO_INTS] = {};  // SpMV only: plan_info written by b200sp_spmv_analyze
+    uint64_t generation = 0;  // BufferGeneration(buffer) when the analysis was written
 };
+
+// Every library call that writes an analysis or scratch data into a caller buffer stamps that buffer with a new
+// generation; a recorded plan is valid only while its generation is still the buffer's current one.  Without it
+// a stale plan would be trusted after its bytes were overwritten: Preprocess(A, buf), then a call that re-analyses
+// into buf for another operation or another matrix, then a compute call on A with buf.
+uint64_t NoteBufferWrite(const void *buffer);   // returns the new generation (never 0)
+uint64_t BufferGeneration(const void *buffer);  // 0 = no library call has written this buffer
 
 }  // namespace b200sp
 

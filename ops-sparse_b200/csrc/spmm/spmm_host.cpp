@@ -50,6 +50,8 @@ aclsparseStatus_t Analyse(const aclsparseSpMatDescr *A, int64_t n, void *buffer,
                           int32_t *segments)
 {
     const size_t bytes = b200sp_spmm_plan_bytes(A->rows, A->nnz, n);
+    // Whatever plan this buffer held is overwritten now; an active plan that is not re-recorded below goes stale.
+    (void)b200sp::NoteBufferWrite(buffer);
     const int rc = b200sp_spmm_analyze(static_cast<const int32_t *>(A->offsets), A->rows, A->nnz, n, buffer, bytes,
                                        segments, stream);
     if (rc != 0) {
@@ -62,7 +64,7 @@ aclsparseStatus_t Analyse(const aclsparseSpMatDescr *A, int64_t n, void *buffer,
 bool PlanMatches(const ActivePlan &p, const void *buffer, const aclsparseSpMatDescr *A, int64_t n)
 {
     return p.kind == PlanKind::kSpmm && p.buffer == buffer && p.rowPtr == A->offsets && p.rows == A->rows &&
-           p.nnz == A->nnz && p.n == n;
+           p.nnz == A->nnz && p.n == n && p.generation == b200sp::BufferGeneration(buffer);
 }
 
 }  // namespace
@@ -109,6 +111,7 @@ aclsparseStatus_t aclsparseSpMMPreprocess(aclsparseHandle_t handle, aclsparseOpe
     p.nnz = matA->nnz;
     p.n = matC->cols;
     p.segments = segments;
+    p.generation = b200sp::BufferGeneration(buffer);
     matA->active = p;
     return ACL_SPARSE_STATUS_SUCCESS;
 }

@@ -33,6 +33,7 @@
 #include <cuda_runtime.h>
 
 #include "b200sp_kernels.h"
+#include "../common/side_stream.h"
 
 namespace {
 
@@ -113,21 +114,50 @@ struct ScalarsI {
     __device__ __forceinline__ int32_t Beta() const { return betaDev ? *betaDev : beta; }
 };
 
+// How the rows of B are fetched.  B is the operand every row of A gathers from: when it fits in L2 (67 MB at
+// 262,144 x 64 fp32) it should stay there while col_ind / values / C stream past it, so its loads carry an
+// L2 evict-last policy (per instruction; nothing outlives the launch) and the streams are evict-first.
+//   0: plain read-only loads   1: read-only loads with L2::evict_last   2: the same without allocating in L1
+#ifndef B200SP_SPMM_B_POLICY
+#define B200SP_SPMM_B_POLICY 1
+#endif
+__device__ __forceinline__ uint4 LoadB16(const void *p)
+{
+#if B200SP_SPMM_B_POLICY == 0
+    return __ldg(reinterpret_cast<const uint4 *>(p));
+#else
+    uint64_t pol;
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));  // hoisted out of loops by the compiler
+    uint4 q;
+#if B200SP_SPMM_B_POLICY == 1
+    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                 : "l"(p), "l"(pol));
+#else
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                 : "l"(p), "l"(pol));
+#endif
+    return q;
+#endif
+}
+
 // 16 bytes of a B row as fp32 values: 4 floats, or 8 half / bf16.
 template <typename T> struct Pack;
 template <> struct Pack<float> {
     static constexpr int kElems = 4;
     static __device__ __forceinline__ void Load(const float *p, float (&out)[4])
     {
-        const float4 q = __ldg(reinterpret_cast<const float4 *>(p));
-        out[0] = q.x; out[1] = q.y; out[2] = q.z; out[3] = q.w;
+        const uint4 q = LoadB16(p);
+        out[0] = __uint_as_float(q.x); out[1] = __uint_as_float(q.y);
+        out[2] = __uint_as_float(q.z); out[3] = __uint_as_float(q.w);
     }
 };
 template <> struct Pack<__half> {
     static constexpr int kElems = 8;
     static __device__ __forceinline__ void Load(const __half *p, float (&out)[8])
     {
-        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint4 q = LoadB16(p);
         const __half2 *h = reinterpret_cast<const __half2 *>(&q);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -141,7 +171,7 @@ template <> struct Pack<__nv_bfloat16> {
     static constexpr int kElems = 8;
     static __device__ __forceinline__ void Load(const __nv_bfloat16 *p, float (&out)[8])
     {
-        const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint4 q = LoadB16(p);
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {  // bf16 -> fp32 is a 16-bit shift
@@ -280,13 +310,29 @@ __device__ __forceinline__ void RowDot(const int32_t *__restrict__ colInd, const
     }
 }
 
+#ifndef B200SP_SPMM_C_STREAMED
+#define B200SP_SPMM_C_STREAMED 1
+#endif
+#if B200SP_SPMM_C_STREAMED
+#define B200SP_SPMM_C_LOAD(p) __ldcs(p)
+#define B200SP_SPMM_C_STORE(p, v) __stcs(p, v)
+#else
+#define B200SP_SPMM_C_LOAD(p) (*(p))
+#define B200SP_SPMM_C_STORE(p, v) (*(p) = (v))
+#endif
 template <typename OutT, int E>
 __device__ __forceinline__ void StoreRowSlice(OutT *dst, const float (&acc)[E], float alpha, float beta)
 {
+    // C is read at most once and written once per product: streamed, so that it does not displace B in L2.
     float z[E];
     if (beta != 0.0f) {
+        constexpr int kVecs = E * (int)sizeof(OutT) / 16;
+        alignas(16) OutT old[E];
 #pragma unroll
-        for (int i = 0; i < E; ++i) z[i] = __fadd_rn(__fmul_rn(alpha, acc[i]), __fmul_rn(beta, ToF32(dst[i])));
+        for (int i = 0; i < kVecs; ++i)
+            reinterpret_cast<uint4 *>(old)[i] = B200SP_SPMM_C_LOAD(reinterpret_cast<const uint4 *>(dst) + i);
+#pragma unroll
+        for (int i = 0; i < E; ++i) z[i] = __fadd_rn(__fmul_rn(alpha, acc[i]), __fmul_rn(beta, ToF32(old[i])));
     } else {
 #pragma unroll
         for (int i = 0; i < E; ++i) z[i] = __fmul_rn(alpha, acc[i]);
@@ -294,13 +340,13 @@ __device__ __forceinline__ void StoreRowSlice(OutT *dst, const float (&acc)[E], 
     if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
         for (int i = 0; i < E; i += 4)
-            *reinterpret_cast<float4 *>(dst + i) = make_float4(z[i], z[i + 1], z[i + 2], z[i + 3]);
+            B200SP_SPMM_C_STORE(reinterpret_cast<float4 *>(dst + i), make_float4(z[i], z[i + 1], z[i + 2], z[i + 3]));
     } else {
         static_assert(E == 8, "16-bit output slices are 8 wide");
         alignas(16) OutT o[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = FromF32<OutT>(z[i]);
-        *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(o);
+        B200SP_SPMM_C_STORE(reinterpret_cast<uint4 *>(dst), *reinterpret_cast<const uint4 *>(o));
     }
 }
 
@@ -917,13 +963,49 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
         a.segs = reinterpret_cast<const SegEntry *>(p + L.offSegs);
         a.counters = reinterpret_cast<int32_t *>(p + L.offCounters);
         a.partials = reinterpret_cast<float *>(p + L.offPartials);
-        int lanes = 1;
-        while (lanes < 32 && lanes * E < sh->n) lanes <<= 1;
-        const long long rowsPerBlock = (long long)kWarps * (32 / lanes);
+        int lanes_ = 1;  // lanes side by side on a row of B
+        while (lanes_ < 32 && lanes_ * E < sh->n) lanes_ <<= 1;
+        const long long rowsPerBlock = (long long)kWarps * (32 / lanes_);
         // B rows of 128 / 256 / 512 bytes: rows of up to kLongRow entries go to the row-stream kernel,
         // and SpmmFastKernel is launched for its segment CTAs only.
         const long long rowBytes = sh->n * (long long)sizeof(ValT);
         const bool stream_ = !sh->kahan && (rowBytes == 512 || rowBytes == 1024) && sh->m > 0 && B200SP_SPMM_USE_STREAM;
+        // With both kernels to run, the segment CTAs (the long rows: few CTAs, each with much work) are forked
+        // onto the side stream first and the row-stream kernel shares the SMs with them.
+        b200sp::SideLanes *lanes = nullptr;
+        cudaStream_t segStream = stream;
+#ifndef B200SP_SPMM_FORK_SEGMENTS
+#define B200SP_SPMM_FORK_SEGMENTS 1
+#endif
+        if (B200SP_SPMM_FORK_SEGMENTS && stream_ && segments > 0) {
+            lanes = b200sp::GetSideLanes();
+            if (lanes != nullptr) {
+                if (cudaEventRecord(lanes->fork, stream) != cudaSuccess ||
+                    cudaStreamWaitEvent(lanes->stream[0], lanes->fork, 0) != cudaSuccess)
+                    return (int)cudaGetLastError();
+                segStream = lanes->stream[0];
+            }
+        }
+        auto launchFast = [&](unsigned grid, cudaStream_t st) {
+            auto launch = [&]<int kLanes>() {
+                if (sh->kahan) SpmmFastKernel<ValT, OutT, true, kLanes><<<grid, kThreads, 0, st>>>(a);
+                else SpmmFastKernel<ValT, OutT, false, kLanes><<<grid, kThreads, 0, st>>>(a);
+                b200sp_note_launches(1);
+            };
+            switch (lanes_) {
+                case 1: launch.template operator()<1>(); break;
+                case 2: launch.template operator()<2>(); break;
+                case 4: launch.template operator()<4>(); break;
+                case 8: launch.template operator()<8>(); break;
+                case 16: launch.template operator()<16>(); break;
+                default: launch.template operator()<32>(); break;
+            }
+        };
+        if (lanes != nullptr) {
+            launchFast((unsigned)segments, segStream);
+            if (cudaGetLastError() != cudaSuccess || cudaEventRecord(lanes->join[0], segStream) != cudaSuccess)
+                return (int)cudaErrorLaunchFailure;
+        }
         if (stream_) {
             StreamArgs<ValT, OutT> sa;
             sa.rowPtr = rowPtr;
@@ -939,23 +1021,12 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
                                            : LaunchRowStream<ValT, OutT, 1024>(sa, stream);
             if (rc != 0) return rc;
         }
+        if (lanes != nullptr)  // the segment CTAs are already running beside the row-stream kernel: join them
+            return (int)cudaStreamWaitEvent(stream, lanes->join[0], 0);
         const long long blocks =
             (long long)segments + (stream_ ? 0 : (sh->m + rowsPerBlock - 1) / rowsPerBlock);
         if (blocks == 0) return 0;
-        const unsigned grid = (unsigned)blocks;
-        auto launch = [&]<int kLanes>() {
-            if (sh->kahan) SpmmFastKernel<ValT, OutT, true, kLanes><<<grid, kThreads, 0, stream>>>(a);
-            else SpmmFastKernel<ValT, OutT, false, kLanes><<<grid, kThreads, 0, stream>>>(a);
-            b200sp_note_launches(1);
-        };
-        switch (lanes) {
-            case 1: launch.template operator()<1>(); break;
-            case 2: launch.template operator()<2>(); break;
-            case 4: launch.template operator()<4>(); break;
-            case 8: launch.template operator()<8>(); break;
-            case 16: launch.template operator()<16>(); break;
-            default: launch.template operator()<32>(); break;
-        }
+        launchFast((unsigned)blocks, stream);
         return (int)cudaGetLastError();
     }
     GenericShape g{sh->m, sh->n, sh->ldb, sh->ldc, sh->order_b == 0, sh->order_c == 0, sh->op_b, sh->kahan};

@@ -156,7 +156,7 @@ constexpr int32_t kTransLongRow = 2048;  // a lane group walks at most this many
 bool PlanMatches(const ActivePlan &p, const void *buffer, const aclsparseSpMatDescr *A)
 {
     return buffer != nullptr && p.kind == PlanKind::kSpmv && p.buffer == buffer && p.rowPtr == A->offsets &&
-           p.rows == A->rows && p.nnz == A->nnz;
+           p.rows == A->rows && p.nnz == A->nnz && p.generation == b200sp::BufferGeneration(buffer);
 }
 
 }  // namespace
@@ -199,6 +199,7 @@ aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, aclsparseOpe
         // The scatter path only wants to know whether some row is far longer than a warp should walk alone.
         ActivePlan t;
         int32_t maxLen = 0;
+        t.generation = b200sp::NoteBufferWrite(externalBuffer);
         const int rcT = b200sp_spmv_max_row_length(static_cast<const int32_t *>(matA->offsets), matA->rows,
                                                    externalBuffer, &maxLen, handle->stream);
         if (rcT != 0) {
@@ -217,6 +218,7 @@ aclsparseStatus_t aclsparseSpMVPreprocess(aclsparseHandle_t handle, aclsparseOpe
     }
     const size_t bytes = b200sp_spmv_plan_bytes(matA->rows, matA->cols, matA->nnz);
     ActivePlan p;
+    p.generation = b200sp::NoteBufferWrite(externalBuffer);
     // Preprocess is the one place that may synchronise: it asks for the binned plan.
     const int rc = b200sp_spmv_analyze(static_cast<const int32_t *>(matA->offsets),
                                        static_cast<const int32_t *>(matA->indices), matA->rows, matA->cols,
@@ -259,20 +261,30 @@ aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOperation_t o
                 return ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES;
             }
         }
-        // A 16-bit y accumulates in the buffer: whatever non-transposed plan was analysed into it is gone.
-        if (scratch == externalBuffer && scratchBytes > 0 && matA->active.buffer == externalBuffer &&
-            matA->active.spmvInfo[0] != kTransPlan)
-            matA->active = ActivePlan{};
-        // Preprocess'ed and a row of kTransLongRow entries or more: cut the scatter by non-zeros.
+        // Preprocess'ed and a row of kTransLongRow entries or more: cut the scatter by non-zeros.  (A transposed
+        // plan is host-side knowledge only, so it survives the accumulator written into the buffer below.)
         const bool byNnz = PlanMatches(matA->active, externalBuffer, matA) &&
                            matA->active.spmvInfo[0] == kTransPlan && matA->active.spmvInfo[1] >= kTransLongRow;
+        // A 16-bit y accumulates in the buffer: whatever analysis any matrix had in it is gone.
+        if (scratch == externalBuffer && scratchBytes > 0) {
+            const uint64_t gen = b200sp::NoteBufferWrite(externalBuffer);
+            if (byNnz) matA->active.generation = gen;
+        }
         rc = b200sp_spmv_trans_launch(rowPtr, colInd, matA->values, vecX->values, vecY->values, matA->rows,
                                       matA->cols, matA->nnz, &sc, c.compType, c.valType, c.outType, scratch,
                                       scratchBytes, byNnz ? 1 : 0, stream);
     } else {
         void *plan = nullptr;
         const int32_t *info = nullptr;
-        if (PlanMatches(matA->active, externalBuffer, matA) && matA->active.spmvInfo[0] != kTransPlan) {
+        const bool active = PlanMatches(matA->active, externalBuffer, matA);
+        if (active && matA->active.spmvInfo[0] == kTransPlan) {
+            // The buffer was sized and analysed for the transposed product (GetBufferSize with op = T may have
+            // returned as little as 256 bytes): a tile plan must not be written into it.
+            B200SP_LOGE("aclsparseSpMV: externalBuffer was preprocessed for the transposed product; "
+                        "run aclsparseSpMVGetBufferSize / Preprocess with ACL_SPARSE_OP_NON_TRANSPOSE");
+            return ACL_SPARSE_STATUS_INVALID_VALUE;
+        }
+        if (active) {
             plan = externalBuffer;  // analysed by Preprocess: nothing to redo
             info = matA->active.spmvInfo;
         } else {
@@ -281,6 +293,7 @@ aclsparseStatus_t aclsparseSpMV(aclsparseHandle_t handle, aclsparseOperation_t o
             if (externalBuffer != nullptr) plan = externalBuffer;
             else if (handle->WorkspaceBytes() >= bytes) plan = handle->Workspace();
             if (plan != nullptr) {
+                (void)b200sp::NoteBufferWrite(plan);  // a plan recorded for this buffer, of any matrix, is stale now
                 rc = b200sp_spmv_analyze(rowPtr, colInd, matA->rows, matA->cols, matA->nnz, plan, bytes, nullptr, stream);
                 if (rc != 0) {
                     B200SP_LOGE("aclsparseSpMV: analysis launch failed (cuda error %d)", rc);

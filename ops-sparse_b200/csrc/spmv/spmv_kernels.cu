@@ -43,6 +43,7 @@
 // values and x are widened to the compute type before the multiply, sums are kept in the
 // compute type, the result is alpha*sum + beta*y rounded once to the output type.
 // beta == 0 never reads y.
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 
@@ -51,6 +52,7 @@
 #include <cuda_runtime.h>
 
 #include "b200sp_kernels.h"
+#include "../common/side_stream.h"
 
 namespace {
 
@@ -72,9 +74,10 @@ constexpr int kVecPerThread = (kTileItems + 6 + 4 * kTileThreads - 1) / (4 * kTi
 
 inline size_t AlignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Rows of at least kLongLen entries form the "long" bin of the binned path (see below).
+// Rows of at least kLongLen entries form the "long" bin of the binned path (see below).  Measured on the
+// 1,048,576-row power-law matrix (us per product): 1024: 95.0, 768: 94.5, 512: 90.6, 384: 104.2.
 #ifndef B200SP_SPMV_LONG_LEN
-#define B200SP_SPMV_LONG_LEN 1024
+#define B200SP_SPMV_LONG_LEN 512
 #endif
 constexpr int kLongLen = B200SP_SPMV_LONG_LEN;
 
@@ -711,7 +714,7 @@ __device__ __forceinline__ void ShortRowsBody(unsigned bid, const int32_t *__res
                                               const Scalars<CompT> &sc)
 {
     const int lane = threadIdx.x & (G - 1);
-    const long long r = ((long long)bid * 256 + threadIdx.x) / G;
+    const long long r = ((long long)bid * blockDim.x + threadIdx.x) / G;
     int s = 0, e = 0;
     if (r < rows) {
         s = rowPtr[r];
@@ -754,7 +757,7 @@ __device__ __forceinline__ void MediumRowsBody(unsigned bid, const int32_t *__re
                                                const Scalars<CompT> &sc)
 {
     const int lane = threadIdx.x & 31;
-    const int i = (int)bid * 8 + (threadIdx.x >> 5);
+    const int i = (int)bid * (int)(blockDim.x >> 5) + (threadIdx.x >> 5);
     if (i >= count) return;  // whole warps leave together
     const int4 ent = __ldg(list + i);
     const int r = ent.x, s = ent.y, e = ent.z;
@@ -872,7 +875,8 @@ __global__ void __launch_bounds__(256) SpmvMediumShortKernel(const int32_t *__re
                                                               const int4 *__restrict__ listM, int nM, int rows,
                                                               Scalars<CompT> sc)
 {
-    const unsigned mediumBlocks = ((unsigned)nM + 7u) >> 3;
+    const unsigned wpc = blockDim.x >> 5;
+    const unsigned mediumBlocks = ((unsigned)nM + wpc - 1u) / wpc;
     if (blockIdx.x < mediumBlocks) MediumRowsBody<CompT, ValT, OutT>(blockIdx.x, colInd, val, x, y, listM, nM, sc);
     else ShortRowsBody<CompT, ValT, OutT, G>(blockIdx.x - mediumBlocks, rowPtr, colInd, val, x, y, rows, sc);
 }
@@ -1085,73 +1089,6 @@ int GroupWidthFor(int64_t rows, int64_t nnz)
     return G;
 }
 
-// One side stream (and the events that fork it from / join it to the caller's stream) per host
-// thread and device, created at first use and destroyed with the thread.  It holds no device
-// memory.  Per thread, because an event recorded by one caller must not be waited on by
-// another caller's side stream.
-struct SideLanes {
-    cudaStream_t stream[1] = {nullptr};
-    cudaEvent_t fork = nullptr;
-    cudaEvent_t join[1] = {nullptr};
-    bool ready = false;
-};
-
-struct SideLaneSet {
-    static constexpr int kMaxDevices = 64;
-    SideLanes lanes[kMaxDevices];
-    ~SideLaneSet()
-    {
-        int prev = 0;
-        const bool havePrev = cudaGetDevice(&prev) == cudaSuccess;
-        for (int d = 0; d < kMaxDevices; ++d) {
-            SideLanes &l = lanes[d];
-            if (!l.ready) continue;
-            if (cudaSetDevice(d) != cudaSuccess) continue;
-            if (l.stream[0] != nullptr) (void)cudaStreamDestroy(l.stream[0]);  // runs what is queued, then frees
-            if (l.join[0] != nullptr) (void)cudaEventDestroy(l.join[0]);
-            if (l.fork != nullptr) (void)cudaEventDestroy(l.fork);
-        }
-        if (havePrev) (void)cudaSetDevice(prev);
-        (void)cudaGetLastError();
-    }
-};
-
-// The side stream gets the highest priority the device offers: its grid is the small one that should be
-// resident first, and (B200SP_SPMV_SIDE_PRIORITY = 0 restores the default) a priority of its own keeps it
-// off the hardware queue of the caller's stream.
-#ifndef B200SP_SPMV_SIDE_PRIORITY
-#define B200SP_SPMV_SIDE_PRIORITY 1
-#endif
-cudaError_t CreateSideStream(cudaStream_t *s)
-{
-#if B200SP_SPMV_SIDE_PRIORITY
-    int least = 0, greatest = 0;
-    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess && greatest < least)
-        return cudaStreamCreateWithPriority(s, cudaStreamNonBlocking, greatest);
-    (void)cudaGetLastError();
-#endif
-    return cudaStreamCreateWithFlags(s, cudaStreamNonBlocking);
-}
-
-SideLanes *GetSideLanes()
-{
-    static thread_local SideLaneSet set;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SideLaneSet::kMaxDevices) return nullptr;
-    SideLanes &l = set.lanes[dev];
-    if (!l.ready) {
-        const bool ok = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess &&
-                        CreateSideStream(&l.stream[0]) == cudaSuccess &&
-                        cudaEventCreateWithFlags(&l.join[0], cudaEventDisableTiming) == cudaSuccess;
-        if (!ok) {
-            (void)cudaGetLastError();
-            return nullptr;  // the caller then runs the kernels on its own stream
-        }
-        l.ready = true;
-    }
-    return &l;
-}
-
 // Binned plan in the caller's buffer: header, list of medium rows, list of long rows and, when
 // the matrix is narrow enough for the blocked long-row kernel, that kernel's tables.
 struct BinLayout {
@@ -1180,16 +1117,16 @@ inline BinLayout BinLayoutFor(int64_t rows, int64_t cols, int64_t nnz)
 }
 
 // plan_info layout shared with the host layer (see b200sp_kernels.h)
-enum { kInfoKind = 0, kInfoMedium = 1, kInfoLong = 2, kInfoGroup = 3 };
+enum { kInfoKind = 0, kInfoMedium = 1, kInfoLong = 2, kInfoGroup = 3, kInfoXBlocks = 4, kInfoBlockElems = 5, kInfoLongLen = 6 };
 enum { kPlanTiles = 0, kPlanBinned = 1, kPlanBinnedBlocked = 2 };  // blocked: long rows go to SpmvLongBlockKernel
 
 template <typename CompT, typename ValT, typename OutT, bool kVec>
 int LaunchLongBlock(const LongBlockArgs<CompT, ValT, OutT> &la, int blocks, cudaStream_t stream)
 {
     constexpr int kSmem = kXBlockElems * (int)sizeof(ValT);
-    static bool configured[SideLaneSet::kMaxDevices] = {};  // per device: this instantiation may use kSmem bytes
+    static bool configured[b200sp::kMaxDevices] = {};  // per device: this instantiation may use kSmem bytes
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SideLaneSet::kMaxDevices) return (int)cudaErrorInvalidDevice;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= b200sp::kMaxDevices) return (int)cudaErrorInvalidDevice;
     if (!configured[dev]) {
         const cudaError_t e = cudaFuncSetAttribute(SpmvLongBlockKernel<CompT, ValT, OutT, kVec>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
@@ -1236,7 +1173,7 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
 #endif
     // The kernels write disjoint rows of y.  The long rows go first, to a side stream forked from
     // and joined back into the caller's stream; medium and short rows follow in one grid.
-    SideLanes *lanes = nL > 0 ? GetSideLanes() : nullptr;
+    b200sp::SideLanes *lanes = nL > 0 ? b200sp::GetSideLanes() : nullptr;
     cudaStream_t sL = stream;
     if (lanes != nullptr) {
         cudaError_t e = cudaEventRecord(lanes->fork, stream);
@@ -1278,19 +1215,23 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
         if (lanes != nullptr) cudaEventRecord(lanes->join[0], sL);
     }
     if (rows > 0) {
-        const unsigned shortBlocks = (unsigned)((rows * G + 255) / 256);
+        // CTAs of kMsThreads threads: a CTA's slot is recycled when its slowest warp is done, and rows of one
+        // CTA differ in length (128 threads: 90.4 us on the power-law matrix, 256: 91.3, 64: 91.8).
+        constexpr int kMsThreads = 128;
+        constexpr int kWpc = kMsThreads / 32;
+        const unsigned shortBlocks = (unsigned)((rows * G + kMsThreads - 1) / kMsThreads);
         if (nM > 0) {
-            const unsigned blocks = (unsigned)((nM + 7) / 8) + shortBlocks;
+            const unsigned blocks = (unsigned)((nM + kWpc - 1) / kWpc) + shortBlocks;
             switch (G) {
-                case 2: SpmvMediumShortKernel<CompT, ValT, OutT, 2><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
-                case 8: SpmvMediumShortKernel<CompT, ValT, OutT, 8><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
-                default: SpmvMediumShortKernel<CompT, ValT, OutT, 4><<<blocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
+                case 2: SpmvMediumShortKernel<CompT, ValT, OutT, 2><<<blocks, kMsThreads, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
+                case 8: SpmvMediumShortKernel<CompT, ValT, OutT, 8><<<blocks, kMsThreads, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
+                default: SpmvMediumShortKernel<CompT, ValT, OutT, 4><<<blocks, kMsThreads, 0, stream>>>(rowPtr, colInd, val, x, y, listM, nM, (int)rows, sc); break;
             }
         } else {
             switch (G) {
-                case 2: SpmvShortRowsKernel<CompT, ValT, OutT, 2><<<shortBlocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
-                case 8: SpmvShortRowsKernel<CompT, ValT, OutT, 8><<<shortBlocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
-                default: SpmvShortRowsKernel<CompT, ValT, OutT, 4><<<shortBlocks, 256, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+                case 2: SpmvShortRowsKernel<CompT, ValT, OutT, 2><<<shortBlocks, kMsThreads, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+                case 8: SpmvShortRowsKernel<CompT, ValT, OutT, 8><<<shortBlocks, kMsThreads, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
+                default: SpmvShortRowsKernel<CompT, ValT, OutT, 4><<<shortBlocks, kMsThreads, 0, stream>>>(rowPtr, colInd, val, x, y, (int)rows, sc); break;
             }
         }
         b200sp_note_launches(1);
@@ -1422,16 +1363,18 @@ extern "C" {
 
 int b200sp_sm_count(void)
 {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            cached = n;
-        else
-            return 148;
+    // one cached value per device ordinal: the GPUs of a process need not be alike
+    static std::atomic<int> cached[b200sp::kMaxDevices] = {};
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    const bool slot = dev >= 0 && dev < b200sp::kMaxDevices;
+    if (slot) {
+        n = cached[dev].load(std::memory_order_relaxed);
+        if (n > 0) return n;
     }
-    return cached;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    if (slot) cached[dev].store(n, std::memory_order_relaxed);
+    return n;
 }
 
 size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz) { return LayoutFor(rows, nnz).total; }
@@ -1504,6 +1447,10 @@ int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t 
     const int minLong = B200SP_SPMV_MIN_LONG_BLOCKED > 48 * L.xBlocks ? B200SP_SPMV_MIN_LONG_BLOCKED : 48 * L.xBlocks;
     const bool useBlocked = blocked && host.unsorted == 0 && host.longs >= minLong;
     plan_info[kInfoKind] = useBlocked ? kPlanBinnedBlocked : kPlanBinned;
+    plan_info[kInfoXBlocks] = useBlocked ? L.xBlocks : 0;
+    plan_info[kInfoBlockElems] = useBlocked ? kXBlockElems : 0;
+    plan_info[kInfoLongLen] = kLongLen;
+    plan_info[7] = 0;
     plan_info[kInfoMedium] = host.medium;
     plan_info[kInfoLong] = host.longs;
 #ifdef B200SP_SPMV_FORCE_SHORT_G
@@ -1572,7 +1519,9 @@ constexpr size_t kNoAllocBytes = 16 * ((size_t)(kNoAllocMaxItems / kTileItems) +
 static __device__ __align__(256) unsigned char gNoAllocScratch[kNoAllocBytes];
 
 constexpr int kMaxDevices = 64;
-void *gNoAllocAddr[kMaxDevices] = {};  // device address of gNoAllocScratch, per device ordinal
+// Device address of gNoAllocScratch, per device ordinal.  Host threads may race to fill a slot; they all
+// store the same address, and the atomic keeps that race defined.
+std::atomic<void *> gNoAllocAddr[kMaxDevices] = {};
 
 // In host code `gNoAllocScratch` is only a handle for the runtime, not an address a kernel can
 // use; the device address has to be asked for, once per device, with that device current.
@@ -1582,13 +1531,13 @@ int NoAllocScratchAddress(void **out)
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
-    if (gNoAllocAddr[dev] == nullptr) {
-        void *p = nullptr;
+    void *p = gNoAllocAddr[dev].load(std::memory_order_relaxed);
+    if (p == nullptr) {
         e = cudaGetSymbolAddress(&p, gNoAllocScratch);
         if (e != cudaSuccess) return (int)e;
-        gNoAllocAddr[dev] = p;
+        gNoAllocAddr[dev].store(p, std::memory_order_relaxed);
     }
-    *out = gNoAllocAddr[dev];
+    *out = p;
     return 0;
 }
 

@@ -383,6 +383,92 @@ void oracle_spmm_abs_sum(const int32_t *row_ptr, const int32_t *col_ind, const v
     }
 }
 
+// ---- whole-result checks at benchmark size -------------------------------------------------
+// The per-row tolerance of the benchmark, |got - gold| <= tol * (|alpha| * sum_j |a_ij * b_j| + |beta * old|),
+// applied to EVERY output of a full-size product without materialising golden or scale arrays (config 5 has
+// 537 M outputs): rows are split over `threads`, every thread forms the golden row (the arithmetic of SpmvRows /
+// SpmmRowsF32 above: fp32 products added in CSR order, then alpha * sum + beta * old) and its fp64 scale and
+// compares.  16-bit inputs are passed widened to fp32, which is exact.  Returns the number of outputs outside
+// the tolerance; *worst receives the largest err / scale seen (0 when every scale is 0 and every error too).
+int64_t oracle_check_spmv_f32(const int32_t *row_ptr, const int32_t *col_ind, const float *val, const float *x,
+                              const float *y_old, const float *got, int64_t rows, float alpha, float beta, double tol,
+                              int threads, double *worst)
+{
+    std::vector<int64_t> bad((size_t)std::max(threads, 1), 0);
+    std::vector<double> worstOf((size_t)std::max(threads, 1), 0.0);
+    const int64_t chunk = threads > 1 ? (rows + threads - 1) / threads : rows;
+    ParallelRows(rows, threads, [&](int64_t lo, int64_t hi) {
+        const size_t slot = chunk > 0 ? (size_t)(lo / chunk) : 0;
+        for (int64_t i = lo; i < hi; ++i) {
+            float sum = 0;
+            double scale = 0.0;
+            for (int32_t j = row_ptr[i]; j < row_ptr[i + 1]; ++j) {
+                sum += val[j] * x[col_ind[j]];
+                scale += std::fabs((double)val[j] * (double)x[col_ind[j]]);
+            }
+            const float old = beta != 0.0f ? y_old[i] : 0.0f;
+            const float z = beta != 0.0f ? alpha * sum + beta * old : alpha * sum;
+            scale = std::fabs((double)alpha) * scale + std::fabs((double)beta * (double)old);
+            const double err = std::fabs((double)got[i] - (double)z);
+            if (!(err <= tol * scale + 1e-37)) ++bad[slot];
+            if (scale > 0.0) worstOf[slot] = std::max(worstOf[slot], err / scale);
+            else if (err > 0.0) worstOf[slot] = INFINITY;
+        }
+    });
+    int64_t total = 0;
+    double w = 0.0;
+    for (size_t t = 0; t < bad.size(); ++t) {
+        total += bad[t];
+        w = std::max(w, worstOf[t]);
+    }
+    if (worst != nullptr) *worst = w;
+    return total;
+}
+
+// Compact row-major B (ldb = n), C_old and got (ldc = n).
+int64_t oracle_check_spmm_f32(const int32_t *row_ptr, const int32_t *col_ind, const float *val, const float *B,
+                              const float *c_old, const float *got, int64_t m, int64_t n, float alpha, float beta,
+                              double tol, int threads, double *worst)
+{
+    std::vector<int64_t> bad((size_t)std::max(threads, 1), 0);
+    std::vector<double> worstOf((size_t)std::max(threads, 1), 0.0);
+    const int64_t chunk = threads > 1 ? (m + threads - 1) / threads : m;
+    ParallelRows(m, threads, [&](int64_t lo, int64_t hi) {
+        const size_t slot = chunk > 0 ? (size_t)(lo / chunk) : 0;
+        std::vector<float> acc((size_t)n);
+        std::vector<double> scale((size_t)n);
+        for (int64_t r = lo; r < hi; ++r) {
+            std::fill(acc.begin(), acc.end(), 0.0f);
+            std::fill(scale.begin(), scale.end(), 0.0);
+            for (int32_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) {
+                const float v = val[p];
+                const float *brow = B + (int64_t)col_ind[p] * n;
+                for (int64_t j = 0; j < n; ++j) {
+                    acc[j] += v * brow[j];
+                    scale[j] += std::fabs((double)v * (double)brow[j]);
+                }
+            }
+            for (int64_t j = 0; j < n; ++j) {
+                const float old = beta != 0.0f ? c_old[r * n + j] : 0.0f;
+                const float z = beta != 0.0f ? alpha * acc[j] + beta * old : alpha * acc[j];
+                const double sc = std::fabs((double)alpha) * scale[j] + std::fabs((double)beta * (double)old);
+                const double err = std::fabs((double)got[r * n + j] - (double)z);
+                if (!(err <= tol * sc + 1e-37)) ++bad[slot];
+                if (sc > 0.0) worstOf[slot] = std::max(worstOf[slot], err / sc);
+                else if (err > 0.0) worstOf[slot] = INFINITY;
+            }
+        }
+    });
+    int64_t total = 0;
+    double w = 0.0;
+    for (size_t t = 0; t < bad.size(); ++t) {
+        total += bad[t];
+        w = std::max(w, worstOf[t]);
+    }
+    if (worst != nullptr) *worst = w;
+    return total;
+}
+
 // ---- verifiers --------------------------------------------------------------------------
 
 // Mixed tolerance of the SpMV harness: pass when at least `ratio` of the elements satisfy

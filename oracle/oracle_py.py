@@ -189,6 +189,34 @@ def spmm_abs_sum(row_ptr, col_ind, val, B, val_type="f32") -> np.ndarray:
     return out
 
 
+# ---- whole-result checks at benchmark size --------------------------------------------------------
+
+def check_spmv_f32(row_ptr, col_ind, val, x, y_old, got, alpha, beta, tol, threads=None):
+    """(outputs outside the per-row tolerance, worst err / scale) of a full-size SpMV result against the golden;
+    val / x widened to fp32 by the caller (exact for 16-bit storage), threaded over rows."""
+    row_ptr, col_ind = _c(row_ptr, np.int32), _c(col_ind, np.int32)
+    val, x, y_old, got = _c(val, np.float32), _c(x, np.float32), _c(y_old, np.float32), _c(got, np.float32)
+    worst = c_double(0.0)
+    f = lib().oracle_check_spmv_f32
+    f.restype = c_int64
+    bad = f(_p(row_ptr), _p(col_ind), _p(val), _p(x), _p(y_old), _p(got), c_int64(row_ptr.size - 1), c_float(alpha),
+            c_float(beta), c_double(tol), int(threads or hardware_threads()), ctypes.byref(worst))
+    return int(bad), float(worst.value)
+
+
+def check_spmm_f32(row_ptr, col_ind, val, B, C_old, got, alpha, beta, tol, threads=None):
+    """The same for SpMM with compact row-major B, C_old and got (all fp32, shapes (k, n), (m, n), (m, n))."""
+    row_ptr, col_ind = _c(row_ptr, np.int32), _c(col_ind, np.int32)
+    val, B, C_old, got = _c(val, np.float32), _c(B, np.float32), _c(C_old, np.float32), _c(got, np.float32)
+    m, n = got.shape
+    worst = c_double(0.0)
+    f = lib().oracle_check_spmm_f32
+    f.restype = c_int64
+    bad = f(_p(row_ptr), _p(col_ind), _p(val), _p(B), _p(C_old), _p(got), c_int64(m), c_int64(n), c_float(alpha),
+            c_float(beta), c_double(tol), int(threads or hardware_threads()), ctypes.byref(worst))
+    return int(bad), float(worst.value)
+
+
 # ---- verifiers --------------------------------------------------------------------------------
 
 MIXED_TOL = {  # rtol, atol, max-abs-error limit, required matched ratio (spmv_test.cpp:208-220)

@@ -189,14 +189,15 @@ def test_buffer_size_formulas(pkg):
     tiles = (rows + nnz + 3839) // 3840  # 256 threads x 15 merge items per tile
     tile_plan = L.b200sp_spmv_tile_plan_bytes(rows, nnz)
     assert 16 * tiles <= tile_plan <= 16 * tiles + 4096   # tile table + counters + two partial arrays, 4 B each
-    # binned plan: a list entry per row that can be longer than 32 entries, one per possible row of 1024+
+    # binned plan: a list entry per row that can be longer than 32 entries, one per possible long row (512+)
     # {row, start, end, -} per entry; the long list twice (as found, then ordered by length)
-    bins = 256 + 16 * (min(rows, nnz // 33) + 1) + 2 * 16 * (nnz // 1024 + 1)
+    long_len = 512
+    bins = 256 + 16 * (min(rows, nnz // 33) + 1) + 2 * 16 * (nnz // long_len + 1)
     # too wide for the blocked long-row kernel (more than 64 blocks of 32768 columns): the lists only
     assert max(tile_plan, bins) <= L.b200sp_spmv_plan_bytes(rows, 1 << 22, nnz) <= max(tile_plan, bins) + 1024
     # narrow enough: per possible long row, xBlocks + 1 cut points and xBlocks partial sums, 4 B each
     xb = (rows + 32767) // 32768
-    blocked = bins + (nnz // 1024 + 1) * (2 * xb + 1) * 4 + 256
+    blocked = bins + (nnz // long_len + 1) * (2 * xb + 1) * 4 + 256
     assert blocked <= L.b200sp_spmv_plan_bytes(rows, rows, nnz) <= blocked + 2048
     assert L.b200sp_spmm_plan_bytes(1 << 18, 1 << 24, 64) >= 2 * ((1 << 24) // 4096) * 64 * 4
 

@@ -142,7 +142,7 @@ def test_csrsort_lets_the_blocked_long_row_kernel_in(pkg, handle, device, oracle
     def kind():
         nb = L.b200sp_spmv_plan_bytes(M, N, A.nnz)
         plan = torch.empty(nb, dtype=torch.uint8, device=device)
-        info = (c_int32 * 4)()
+        info = (c_int32 * 8)()  # B200SP_SPMV_PLAN_INFO_INTS
         assert L.b200sp_spmv_analyze(c_void_p(d_rp.data_ptr()), c_void_p(d_ci.data_ptr()), M, N, A.nnz,
                                      c_void_p(plan.data_ptr()), nb, info, None) == 0
         return info[0]

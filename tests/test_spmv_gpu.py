@@ -167,7 +167,7 @@ def plan_kind(pkg, device, rp, ci, cols):
     d_rp, d_ci = torch.from_numpy(rp).to(device), torch.from_numpy(ci).to(device)
     nb = L.b200sp_spmv_plan_bytes(rows, cols, nnz)
     plan = torch.empty(nb, dtype=torch.uint8, device=device)
-    info = (c_int32 * 4)()
+    info = (c_int32 * 8)()
     assert L.b200sp_spmv_analyze(c_void_p(d_rp.data_ptr()), c_void_p(d_ci.data_ptr()), rows, cols, nnz,
                                  c_void_p(plan.data_ptr()), nb, info, None) == 0
     torch.cuda.synchronize()
@@ -183,16 +183,16 @@ def many_long_rows(rng, M, N, n_long, lo=1024, hi=6000):
 
 @pytest.mark.parametrize("vt,ot", [("f32", "f32"), ("f16", "f32"), ("bf16", "bf16"), ("i32", "i32")])
 def test_long_rows_take_the_column_blocked_kernel(handle, device, oracle, pkg, vt, ot):
-    """Many rows of 1024+ entries spread over five blocks of x (the last one partial), next to short rows,
-    rows of exactly 1023 / 1024 entries and very long ones."""
+    """Many long rows spread over five blocks of x (the last one partial), next to short rows, rows just
+    below and at the long-row threshold (511 / 512 entries) and very long ones."""
     rng = np.random.default_rng(21)
     M, N = 3000, 150000
     lengths, _ = many_long_rows(rng, M, N, 260)  # five column blocks of x: 48 long rows per block at least
-    for r, L in zip((0, 7, 500, 501, 1999, 2999), (1024, 1023, 1500, 5000, 20000, 60000)):
+    for r, L in zip((0, 7, 500, 501, 1999, 2999, 30, 31), (1024, 1023, 1500, 5000, 20000, 60000, 512, 511)):
         lengths[r] = L
     rp, ci = random_csr(rng, M, N, lengths)
     info = plan_kind(pkg, device, rp, ci, N)
-    assert info[0] == 2 and info[2] == int((lengths >= 1024).sum())
+    assert info[0] == 2 and info[2] == int((lengths >= info[6]).sum())
     val, x, y = draw(rng, oracle, rp[-1], vt), draw(rng, oracle, N, vt), draw(rng, oracle, M, ot)
     a, b = (2, -1) if ot == "i32" else (1.5, 0.5)
     for mode in ("plan", "workspace"):  # Preprocess routes long rows away; the per-call analysis does not
@@ -349,8 +349,18 @@ def test_golden_fixture_spmv(handle, device, oracle, golden_dir):
                        z[f"{i}/y"], a, b, vt, ot, trans=bool(trans), rows=M, cols=N)
         gold = z[f"{i}/gold"]
         if trans and ot in ("f16", "bf16"):
-            # golden with per-update 16-bit rounding: the reference harness has no device case of
-            # this kind, and the kernel (fp32 accumulation) is checked in test_type_triples instead
+            # Transposed product with a 16-bit y: the golden rounds its running sums to 16 bits after every
+            # update (a combination the reference harness never runs on a device: its transposed
+            # mixed-precision cases have an fp32 y), the kernel accumulates in fp32 and rounds once.  Against the
+            # stored golden the harness's mixed-tolerance verdict fails for either of them being "right" (93 % of
+            # the fp16 outputs within tolerance: the golden carries its own rounding noise), so the verdict is
+            # taken against the same golden function run with an fp32 y and rounded once.
+            y32 = oracle.from_storage(z[f"{i}/y"], ot).astype(np.float32)
+            g32 = oracle.spmv_typed(z[f"{i}/row_ptr"], z[f"{i}/col_ind"], z[f"{i}/val"], z[f"{i}/x"], y32, a, b, comp,
+                                    vt, "f32", trans=True, cols=N)
+            once = oracle.from_storage(oracle.to_storage(g32, ot), ot)
+            ok, st = oracle.verify_mixed(once, oracle.from_storage(got, ot), ot)
+            assert ok, (i, comp, vt, ot, "rounded once", st)
             continue
         if ot == "i32":
             assert np.array_equal(got, gold), i
@@ -410,3 +420,67 @@ def test_transposed_power_law_rows_cut_by_non_zeros(handle, device, oracle, vt, 
         got = run_spmv(handle, device, oracle, rp, ci, val, x, y, a, b, vt, ot, trans=True, rows=M, cols=N, mode=mode)
         check_against_oracle(oracle, rp, ci, val, x, y, a, b, vt, ot, got, trans=True, cols=N,
                              what=f"transposed power law {vt}/{mode}")
+
+
+def _power_law_case(oracle, seed, rows, cols):
+    from ops_sparse_b200 import synth
+    rng = np.random.default_rng(seed)
+    lengths = synth.zipf_lengths(rng, rows, 1.8, min(cols, 5000), 20.0)
+    A = synth.csr_from_lengths(rng, lengths, cols, synth.normal)
+    return A, rng.standard_normal(cols).astype(np.float32), rng.standard_normal(rows).astype(np.float32)
+
+
+def test_stale_plans_are_not_trusted(handle, device, oracle):
+    """One workspace reused across matrices and operations: a plan whose bytes a later call overwrote must be
+    rebuilt, not run.  (1) Preprocess(A, buf), Preprocess(B, buf), SpMV(A, buf);  (2) SpMMPreprocess(A, buf),
+    SpMV(A, buf) -- which writes a tile plan into buf --, SpMM(A, buf)."""
+    from ops_sparse_b200 import api
+    A, xa, ya = _power_law_case(oracle, 21, 9000, 7000)
+    B, xb, yb = _power_law_case(oracle, 22, 6000, 7000)
+    dA = helpers.make_csr(device, A.row_ptr, A.col_ind, A.values, "f32", A.rows, A.cols)
+    dB = helpers.make_csr(device, B.row_ptr, B.col_ind, B.values, "f32", B.rows, B.cols)
+    dxa, dya = api.DnVec(torch.from_numpy(xa).to(device)), api.DnVec(torch.from_numpy(ya).to(device))
+    dxb, dyb = api.DnVec(torch.from_numpy(xb).to(device)), api.DnVec(torch.from_numpy(yb).to(device))
+    n = 16
+    rng = np.random.default_rng(23)
+    Bd = rng.standard_normal((A.cols, n)).astype(np.float32)
+    Cd = rng.standard_normal((A.rows, n)).astype(np.float32)
+    dBm, dCm = api.DnMat.row_major(torch.from_numpy(Bd).to(device)), api.DnMat.row_major(torch.from_numpy(Cd).to(device))
+    need = max(api.spmv_buffer_size(handle, dA, dxa, dya), api.spmv_buffer_size(handle, dB, dxb, dyb),
+               api.spmm_buffer_size(handle, dA, dBm, dCm))
+    buf = torch.empty(need, dtype=torch.uint8, device=device)
+    L, S = api.lib(), api
+    from ops_sparse_b200 import ACL_FLOAT
+    pre = lambda M, x, y: api.check(L.aclsparseSpMVPreprocess(handle.raw, 0, None, M.raw, x.raw, None, y.raw, ACL_FLOAT,
+                                                              0, api._ptr(buf)), "aclsparseSpMVPreprocess")
+    pre(dA, dxa, dya)
+    pre(dB, dxb, dyb)
+    api.spmv(handle, dA, dxa, dya, 1.25, -0.5, buffer=buf)
+    torch.cuda.synchronize()
+    gold = oracle.spmv(A.row_ptr, A.col_ind, A.values, xa, ya, 1.25, -0.5)
+    scale = 1.25 * oracle.spmv_abs_rowsum(A.row_ptr, A.col_ind, A.values, xa) + np.abs(0.5 * ya)
+    helpers.assert_rowwise(dya.values.cpu().numpy().astype(np.float64), gold, scale, helpers.TOL["f32"],
+                           "SpMV(A) after Preprocess(B) into the same buffer")
+    # (2)
+    api.check(L.aclsparseSpMMPreprocess(handle.raw, 0, 0, None, dA.raw, dBm.raw, None, dCm.raw, ACL_FLOAT, 0,
+                                        api._ptr(buf)), "aclsparseSpMMPreprocess")
+    dya2 = api.DnVec(torch.from_numpy(ya).to(device))
+    api.spmv(handle, dA, dxa, dya2, 1.0, 0.0, buffer=buf)
+    api.spmm(handle, dA, dBm, dCm, 0.5, 2.0, buffer=buf)
+    torch.cuda.synchronize()
+    goldC = oracle.spmm_f32(A.row_ptr, A.col_ind, A.values, Bd, Cd, 0.5, 2.0)
+    scaleC = 0.5 * oracle.spmm_abs_sum(A.row_ptr, A.col_ind, A.values, Bd) + np.abs(2.0 * Cd)
+    helpers.assert_rowwise(dCm.values.cpu().numpy().astype(np.float64), goldC, scaleC, helpers.TOL["f32"],
+                           "SpMM(A) after SpMV(A) re-analysed the shared buffer")
+
+
+def test_plain_product_refuses_a_buffer_preprocessed_for_the_transpose(handle, device, pkg, oracle):
+    from ops_sparse_b200 import api, ACL_SPARSE_OP_TRANSPOSE, ACL_FLOAT
+    A, x, y = _power_law_case(oracle, 24, 3000, 3000)
+    dA = helpers.make_csr(device, A.row_ptr, A.col_ind, A.values, "f32", A.rows, A.cols)
+    dx, dy = api.DnVec(torch.from_numpy(x).to(device)), api.DnVec(torch.from_numpy(y).to(device))
+    buf = api.spmv_preprocess(handle, dA, dx, dy, ACL_SPARSE_OP_TRANSPOSE)  # 256 bytes for an fp32 y
+    rc = pkg.lib().aclsparseSpMV(handle.raw, 0, None, dA.raw, dx.raw, None, dy.raw, ACL_FLOAT, 0, api._ptr(buf))
+    assert rc == pkg.ACL_SPARSE_STATUS_INVALID_VALUE
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(dy.values.cpu().numpy(), y)  # nothing ran

@@ -77,3 +77,38 @@ def test_refuses_a_matrix_beyond_its_fixed_scratch(pkg, device):
     assert rc != 0
     torch.cuda.synchronize()  # the context is still healthy
     assert float(f.sum().item()) == 0.0
+
+
+def test_unaligned_arrays_and_empty_matrix(pkg, device, oracle):
+    """col_ind / val that start one element past a 16-byte boundary take the scalar-load form of the kernel;
+    a matrix without entries must still give y = beta * y."""
+    noalloc = _fn(pkg)
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    A, x, y, d_rp, d_ci, d_v, d_x = _case(3, 12000, 15000, device)
+    shifted_ci = torch.empty(A.nnz + 1, dtype=torch.int32, device=device)
+    shifted_v = torch.empty(A.nnz + 1, dtype=torch.float32, device=device)
+    shifted_ci[1:].copy_(d_ci)
+    shifted_v[1:].copy_(d_v)
+    assert shifted_ci[1:].data_ptr() % 16 == 4
+    y2 = torch.from_numpy(y).to(device)
+    rc = noalloc(c_void_p(d_rp.data_ptr()), c_void_p(shifted_ci[1:].data_ptr()), c_void_p(shifted_v[1:].data_ptr()),
+                 c_void_p(d_x.data_ptr()), c_void_p(y2.data_ptr()), A.rows, A.cols, A.nnz, 2.0, -0.5, stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    gold = oracle.spmv(A.row_ptr, A.col_ind, A.values, x, y, 2.0, -0.5)
+    scale = 2.0 * oracle.spmv_abs_rowsum(A.row_ptr, A.col_ind, A.values, x) + np.abs(0.5 * y)
+    helpers.assert_rowwise(y2.cpu().numpy().astype(np.float64), gold, scale, helpers.TOL["f32"], "noalloc, unaligned")
+
+    rows = 5000
+    zero_rp = torch.zeros(rows + 1, dtype=torch.int32, device=device)
+    pad = torch.zeros(4, dtype=torch.float32, device=device)
+    y3 = torch.from_numpy(y[:rows].copy()).to(device)
+    rc = noalloc(c_void_p(zero_rp.data_ptr()), c_void_p(zero_rp.data_ptr()), c_void_p(pad.data_ptr()),
+                 c_void_p(d_x.data_ptr()), c_void_p(y3.data_ptr()), rows, A.cols, 0, 1.0, 0.25, stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(y3.cpu().numpy(), (np.float32(0.25) * y[:rows]).astype(np.float32))
+    rc = noalloc(c_void_p(zero_rp.data_ptr()), c_void_p(zero_rp.data_ptr()), c_void_p(pad.data_ptr()),
+                 c_void_p(d_x.data_ptr()), c_void_p(y3.data_ptr()), 0, A.cols, 0, 1.0, 0.25, stream)
+    assert rc == 0  # no rows: nothing to do, nothing launched
+    torch.cuda.synchronize()
