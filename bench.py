@@ -1,28 +1,31 @@
 """Benchmark of the CSR SpMV / SpMM hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c1..c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2] [--configs c1,...]
 
-Default workload (c2): CSR SpMV fp32 on a 1,048,576 x 1,048,576 matrix with power-law row lengths
+Headline workload (c2): CSR SpMV fp32 on a 1,048,576 x 1,048,576 matrix with power-law row lengths
 (Zipf s = 1.8, mean about 30, cap 16384, about 30 M non-zeros), y = 1.5 A x + 0.5 y.  All inputs
 are seeded synthetic data (no matrix collection is read).  One "step" is one such product.
 
-Our arm prints one JSON line with
+Our arm prints ONE JSON line.  Its top-level keys describe the headline configuration:
   value          GFLOP/s (2 * nnz * N per step) with every input resident in HBM, CUDA-event timed
-  e2e            the same metric through the aclsparse C API with x and y in pinned HOST memory:
-                 x and y are copied to the device, aclsparseSpMV runs, y is copied back, every step
-                 (A stays resident and analysed once, as the API's Preprocess contract intends)
+  e2e            the same metric through the aclsparse C API with x / B and y / C in pinned HOST memory:
+                 copied to the device, multiplied, copied back, every step (A stays resident and analysed
+                 once, as the API's Preprocess contract intends)
   roofline       algorithmic bytes per launch / measured launch time, against the measured HBM peak
-  cpu_baseline   the reference's own CPU golden timed on this host's cores
-`--impl reference` times that CPU golden alone (all host threads) and prints the same line shape.
+  cpu_baseline   the reference's own CPU golden timed on this host's cores (all threads, and one)
+  parity_full    every output of the last end-to-end step checked against the CPU oracle
+and `configs` holds the same measurements for every benchmark configuration that was run (all five on one
+GPU; c2 and c5 on several).  `--impl reference` times the CPU golden alone and prints the same line shape.
 
 With --gpus N > 1 (launched by torchrun, one rank per GPU) the matrix is cut into N row blocks of
-equal non-zero count (strong scaling: the total work is fixed), x is broadcast from rank 0 over
-NCCL inside every timed step, y stays sharded; time is the maximum over ranks.
+equal non-zero count (strong scaling: the total work is fixed), x / B is held in N slices (rank r owns
+slice r) and replicated inside every timed step, y / C stays sharded; time is the maximum over ranks.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes
+import gc
 import json
 import os
 import sys
@@ -38,6 +41,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
 NOMINAL_HBM_GBS = 8000.0
+ALL_CONFIGS = ("c1", "c2", "c3", "c4", "c5")
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -51,7 +55,7 @@ def measured_peaks() -> tuple[float, str]:
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML (read-only) while a timed region runs."""
 
     def __init__(self, index: int):
         super().__init__(daemon=True)
@@ -121,7 +125,8 @@ def build_config(name: str, synth):
             "c5": synth.config5}[name]()
 
 
-def describe(name: str, cfg) -> dict:
+def describe(cfg) -> dict:
+    """The workload, in the same words for both arms (the driver compares this object between them)."""
     A = cfg["A"]
     d = {"workload": cfg["name"], "rows": A.rows, "cols": A.cols, "nnz": A.nnz, "alpha": cfg["alpha"],
          "beta": cfg["beta"], "values": cfg["val"], "output": cfg["out"], "index": "int32",
@@ -141,6 +146,14 @@ def bytes_and_flops(cfg, synth, rows=None, nnz=None):
         n = cfg["B"].shape[1]
         return synth.algorithmic_bytes_spmm(rows, A.cols, nnz, n, vb, ob, cfg["beta"]), 2.0 * nnz * n
     return synth.algorithmic_bytes_spmv(rows, A.cols, nnz, vb, ob, cfg["beta"]), 2.0 * nnz
+
+
+def metric_name(cfg) -> str:
+    return "csr_spmm_gflops" if "B" in cfg else "csr_spmv_gflops"
+
+
+def dtype_name(cfg) -> str:
+    return {"f32": "f32", "f16": "f16 values, f32 accumulate", "bf16": "bf16 values, f32 accumulate"}[cfg["val"]]
 
 
 # ------------------------------------------------------------------------------- CPU arm
@@ -185,113 +198,112 @@ class CpuGolden:
         sec, nnz = self.run(rows, reps)
         return {"value": 2.0 * nnz * self.n / sec / 1e9, "unit": "GFLOP/s", "cores": self.threads, "kind": self.kind,
                 "sample": f"rows [0, {rows}) of {self.A.rows} ({nnz} of {self.A.nnz} nnz), {reps} passes, "
-                          f"{sec * 1e3:.2f} ms per pass; 16-bit configurations are timed on fp32-widened values",
+                          f"{sec * 1e3:.2f} ms per pass; 16-bit configurations are timed on fp32-widened values; "
+                          "the golden's row loop is split statically over the threads (started and joined inside "
+                          "every clocked pass, as a caller of the reference's loop would)",
                 "ms_per_pass": sec * 1e3}
 
 
-def cpu_baseline(cfg, oracle, threads: int, budget_s: float = 12.0) -> dict:
+def cpu_baseline(cfg, oracle, threads: int, budget_s: float = 6.0) -> dict:
     """At most about `budget_s` seconds of wall time on all host threads: the whole matrix when a pass is
     short (repeated until about a second has been spent), else its leading rows, 3 passes.  The same loop
     on one thread (the golden as the reference's harness runs it) is timed beside it on a sample a
     tenth as long."""
     g = CpuGolden(cfg, oracle, threads)
-    rows = g.rows_for(budget_s / 3)
+    rows = g.rows_for(budget_s / 4)
     sec, _ = g.run(rows, 1)  # also the warm-up pass
     reps = int(min(200, max(3, round(1.0 / max(sec, 1e-4)))))
     rep = g.report(rows, reps)
     one = CpuGolden(cfg, oracle, 1)
-    rows1 = one.rows_for(budget_s / 30)
+    rows1 = one.rows_for(budget_s / 40)
     one.run(rows1, 1)
     r1 = one.report(rows1, 3)
-    rep["single_core"] = {"value": r1["value"], "unit": r1["unit"], "sample": r1["sample"]}
+    rep["single_core"] = {"value": r1["value"], "unit": r1["unit"], "cores": 1, "kind": r1["kind"],
+                          "sample": r1["sample"]}
     return rep
+
+
+def reference_config(name: str, args, synth, oracle, steps: int, warmup: int, wall_budget_s: float) -> dict:
+    cfg = build_config(name, synth)
+    g = CpuGolden(cfg, oracle, oracle.hardware_threads())
+    # one step = one golden pass over a bounded sample; warm-up + steps must end within the budget
+    per_step = max(0.002, min(4.0, wall_budget_s / max(steps + warmup, 1)))
+    rows = g.rows_for(per_step)
+    t0 = time.perf_counter()
+    per, nnz = g.passes(rows, warmup + steps)  # W untimed passes, then exactly K timed ones
+    wall = time.perf_counter() - t0
+    timed = per[warmup:]
+    sec = float(timed.mean())
+    v = 2.0 * nnz * g.n / sec / 1e9
+    return {
+        "metric": metric_name(cfg), "value": v, "unit": "GFLOP/s", "steps": steps, "warmup": warmup,
+        "ms_per_step": sec * 1e3,
+        "per_step_ms": {"min": float(timed.min()) * 1e3, "median": float(np.median(timed)) * 1e3,
+                        "max": float(timed.max()) * 1e3},
+        "dtype": dtype_name(cfg), "config": describe(cfg),
+        "cpu_baseline": {"value": v, "unit": "GFLOP/s", "cores": g.threads, "kind": g.kind,
+                         "sample": f"rows [0, {rows}) of {g.A.rows} ({nnz} of {g.A.nnz} nnz) per step; the clock "
+                                   f"covers the golden loop only (whole run {wall:.1f} s with argument set-up); "
+                                   "threads are started and joined inside every clocked pass"},
+        "e2e": {"value": v, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
 
 
 def reference_arm(args, synth, oracle):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return  # the CPU golden runs once per job: the other ranks have nothing to do
-    cfg = build_config(args.config, synth)
-    g = CpuGolden(cfg, oracle, oracle.hardware_threads())
-    # one step = one golden pass over a bounded sample; K + W steps must end within a few minutes
-    per_step = max(0.002, min(4.0, 150.0 / max(args.steps + args.warmup, 1)))
-    rows = g.rows_for(per_step)
-    t0 = time.perf_counter()
-    per, nnz = g.passes(rows, args.warmup + args.steps)  # W untimed passes, then exactly K timed ones
-    wall = time.perf_counter() - t0
-    sec = float(per[args.warmup:].mean())
-    v = 2.0 * nnz * g.n / sec / 1e9
-    line = {
-        "impl": "reference", "metric": metric_name(cfg), "value": v, "unit": "GFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": dtype_name(cfg), "data": "synthetic (seeded)",
-        "config": describe(args.config, cfg),
-        "cpu_baseline": {"value": v, "unit": "GFLOP/s", "cores": g.threads, "kind": g.kind,
-                         "sample": f"rows [0, {rows}) of {g.A.rows} ({nnz} of {g.A.nnz} nnz) per step; the clock "
-                                   f"covers the golden loop only (whole run {wall:.1f} s with argument set-up)"},
-        "e2e": {"value": v, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
+    names = config_list(args, 1 if args.gpus <= 1 else args.gpus)
+    results = {}
+    for name in names:
+        head = name == args.config
+        steps, warmup = (args.steps, args.warmup) if head else (min(args.steps, 5), 3)
+        results[name] = reference_config(name, args, synth, oracle, steps, warmup, 120.0 if head else 25.0)
+    h = results[args.config]
+    line = {"impl": "reference", "metric": h["metric"], "value": h["value"], "unit": "GFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": h["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": h["dtype"], "data": "synthetic (seeded)",
+            "config": h["config"], "cpu_baseline": h["cpu_baseline"], "e2e": h["e2e"], "gpu_launches": 0,
+            "per_step_ms": h["per_step_ms"], "configs": results}
     print(json.dumps(line))
 
 
-def metric_name(cfg) -> str:
-    return "csr_spmm_gflops" if "B" in cfg else "csr_spmv_gflops"
-
-
-def dtype_name(cfg) -> str:
-    return {"f32": "f32", "f16": "f16 values, f32 accumulate", "bf16": "bf16 values, f32 accumulate"}[cfg["val"]]
+def config_list(args, world: int) -> list[str]:
+    if args.configs:
+        names = [c for c in args.configs.split(",") if c]
+    else:
+        names = list(ALL_CONFIGS) if world == 1 else ["c2", "c5"]
+    if args.config not in names:
+        names.insert(0, args.config)
+    return names
 
 
 # ------------------------------------------------------------------------------- GPU arm
 
-# DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum +
-# dram__bytes_write.sum); filled from the summaries committed under profiles/.  None = not captured.
-NCU_TRAFFIC_BYTES = {
-    "c2": 284_459_008,  # both kernels of one product: 147.7 MB (long rows) + 136.8 MB (medium + short rows)
-    "c3": 353_516_032,
-    "c4": 641_619_968,
+# DRAM bytes per product from ncu captures on one GPU (dram__bytes_read.sum + dram__bytes_write.sum, summed over
+# the kernels of one product), with the summary under profiles/ they were read from.  A figure is attached to a
+# line only when the kernels that ran are the ones the capture covers.
+NCU_TRAFFIC = {
+    "c2": {"bytes": 287_100_000, "kernels": "SpmvLongBlockKernel + SpmvMediumShortKernel",
+           "source": "profiles/spmv_binned_c2_powerlaw_f32.md"},
+    "c3": {"bytes": 353_516_032, "kernels": "SpmvShortRowsKernel", "source": "profiles/spmv_binned_c3_stencil27_f16.md"},
+    "c4": {"bytes": 641_619_968, "kernels": "SpmmFastKernel", "source": "profiles/spmm_fast_c4_f32_n64.md"},
+    "c5": {"bytes": 18_800_000_000, "kernels": "SpmmRowStreamKernel + SpmmFastKernel",
+           "source": "profiles/spmm_rowstream_c5_bf16_n256.md"},
 }
 # What the counters show to be the busy resource where it is not DRAM.
 BOUND_NOTES = {
-    "c2": "x gathers from uniformly random columns cost one 32-byte L2 sector request each and an SM issues one "
-          "request per clock: the medium + short kernel keeps that port 74 % busy (DRAM 25 %); the long rows "
-          "(56 % of the non-zeros) gather from x blocks staged in shared memory and run beside it",
-    "c4": "B (67 MB) is gathered from L2: 4.48 GB through L2->L1 per product, L2 slices 71 % and L1 78 % busy",
-    "c5": "B (1.07 GB) exceeds L2: the row gather is DRAM traffic, about 18.8 GB per product (5.5 x the algorithmic "
-          "bytes, which count B once); against that traffic the product runs at about 6.4 TB/s",
+    "c1": "0.57 MB of inputs, L2-resident: a product is one launch of a few microseconds, bandwidth fractions say "
+          "nothing here",
+    "c2": "every gather of x from a random column is one 32-byte sector request to L2 and an SM issues one request "
+          "per clock (measured: 0.97-0.99 gathers per clock and SM); the rows of 512+ entries (64 % of the "
+          "non-zeros) gather from blocks of x staged in shared memory instead, beside the other rows' grid",
+    "c4": "B (67 MB) is gathered from L2: 4.3 GB move L2->SM per product and that path delivers 18.1-18.4 TB/s "
+          "(62-63 B per clock and SM, measured with a pure row-gather probe), so 236 us is the floor of any "
+          "formulation that fetches a B row per non-zero",
+    "c5": "B (1.07 GB) exceeds L2: the row gather is DRAM traffic, about 5.5 x the algorithmic bytes (which count "
+          "B once); against that traffic the product runs at about 6.3 TB/s",
 }
-
-
-def dominant_kernels(is_spmm: bool, launches_per_step: float, b_row_bytes: int) -> str:
-    """The kernels one step launches, as the library's routing rules give them."""
-    if is_spmm:
-        if b_row_bytes in (512, 1024):
-            return ("SpmmRowStreamKernel (rows <= 1024 nnz)" +
-                    (" + SpmmFastKernel (segment CTAs of longer rows)" if launches_per_step > 1 else ""))
-        return "SpmmFastKernel"
-    if launches_per_step > 1:
-        return "SpmvLongBlockKernel | SpmvLongListKernel (side stream) + SpmvMediumShortKernel"
-    return "SpmvShortRowsKernel | SpmvMediumShortKernel"
-
-
-class SpMVOpStep:
-    """The same product through the SpMVOp plan API (compensated row sums), Z aliasing Y; `step` like the
-    sharded operators so that the timing loops do not care."""
-
-    def __init__(self, d_rp, d_ci, d_v, cols, x, y, alg):
-        from ops_sparse_b200 import api
-        self.h = api.Handle()
-        self.A = api.CsrMatrix(d_rp, d_ci, d_v, d_rp.numel() - 1, cols)
-        self.x, self.y = api.DnVec(x), api.DnVec(y)
-        self.plan = api.SpMVOpPlan(self.h, self.A, self.x, self.y, self.y, alg=alg)
-
-    def step(self, alpha, beta, broadcast=False):
-        self.plan.run(self.x, self.y, self.y, alpha, beta)
-
-    def close(self):
-        self.plan.close()
-        self.h.close()
 
 
 def torch_dtype(kind: str):
@@ -299,23 +311,34 @@ def torch_dtype(kind: str):
     return {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[kind]
 
 
-def gpu_arm(args, synth, oracle):
+class Env:
+    pass
+
+
+def kernels_of(is_spmm: bool, launches_per_step: float, b_row_bytes: int, world: int) -> str:
+    """The kernels one step launches, as the library's routing rules give them."""
+    if is_spmm:
+        if b_row_bytes in (512, 1024):
+            return ("SpmmRowStreamKernel" + (" + SpmmFastKernel (segment CTAs of rows > 1024 nnz, side stream)"
+                                             if launches_per_step > 1 + (world > 1) else ""))
+        return "SpmmFastKernel"
+    if launches_per_step >= 2 + (world > 1):
+        return "SpmvLongBlockKernel (side stream) + SpmvMediumShortKernel"
+    return "SpmvShortRowsKernel | SpmvMediumShortKernel | SpmvAllBinsKernel"
+
+
+def measure_config(name: str, args, env, head: bool) -> dict:
+    """Every leg of the benchmark for one configuration on this rank's share; returns the rank-0 result dict
+    (other ranks return their local pieces, which the caller ignores)."""
     import torch
     import torch.distributed as dist
+    from ops_sparse_b200 import api, hostio, mg
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the product path has no CPU implementation")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    from ops_sparse_b200 import mg
-    pkg = entry.load_package()
+    torch_, world, rank, dev, oracle, synth, pkg = env.torch, env.world, env.rank, env.dev, env.oracle, env.synth, env.pkg
+    L = pkg.lib()
+    K, W = (args.steps, args.warmup) if head else (min(args.steps, 200), min(args.warmup, 10))
 
-    cfg = build_config(args.config, synth)  # every rank draws the same matrix from the same seed
+    cfg = build_config(name, synth)  # every rank draws the same matrix from the same seed
     A = cfg["A"]
     is_spmm = "B" in cfg
     alpha, beta = cfg["alpha"], cfg["beta"]
@@ -325,31 +348,47 @@ def gpu_arm(args, synth, oracle):
     rp, ci, v = mg.slice_csr(A.row_ptr, A.col_ind, A.values, r0, r1)
     d_rp, d_ci = torch.from_numpy(rp).to(dev), torch.from_numpy(np.ascontiguousarray(ci)).to(dev)
     d_v = torch.from_numpy(np.ascontiguousarray(v)).to(dev).to(vt)
-    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    replicate = args.replicate if world > 1 else "none"
     if is_spmm:
         n = cfg["B"].shape[1]
-        dense_h = pin(cfg["B"]).to(vt) if False else torch.from_numpy(cfg["B"]).to(vt).pin_memory()
+        dense_h = torch.from_numpy(cfg["B"]).to(vt).pin_memory()
         out_h = torch.from_numpy(cfg["C"][r0:r1]).to(ot).pin_memory()
-        dense = dense_h.to(dev) if rank == 0 else torch.zeros_like(dense_h, device=dev)
-        out = out_h.to(dev)
-        op = mg.ShardedSpmm(d_rp, d_ci, d_v, A.cols, dense, out)
     else:
         n = 1
         dense_h = torch.from_numpy(cfg["x"]).to(vt).pin_memory()
         out_h = torch.from_numpy(cfg["y"][r0:r1]).to(ot).pin_memory()
-        dense = dense_h.to(dev) if rank == 0 else torch.zeros_like(dense_h, device=dev)
-        out = out_h.to(dev)
-        op = mg.ShardedSpmv(d_rp, d_ci, d_v, A.cols, dense, out)
-        if args.api != "spmv":
-            if cfg["val"] != "f32" or world > 1:
-                raise SystemExit("--api spmvop-alg1 / spmvop-alg2: fp32 SpMV configurations (c1, c2), one GPU")
-            op.close()
-            op = SpMVOpStep(d_rp, d_ci, d_v, A.cols, dense, out, 2 if args.api == "spmvop-alg2" else 1)
+    # Every rank starts from the whole operand only to cut its own slice from it (the sharded operators keep
+    # that slice); in the "nccl-broadcast" form the other ranks' copies are zeroed so that the step must fill them.
+    dense = dense_h.to(dev)
+    if world > 1 and replicate == "nccl-broadcast" and rank != 0:
+        dense.zero_()
+    out = out_h.to(dev)
+    if is_spmm:
+        op = mg.ShardedSpmm(d_rp, d_ci, d_v, A.cols, dense, out, replicate=replicate if world > 1 else "nccl-broadcast")
+    else:
+        op = mg.ShardedSpmv(d_rp, d_ci, d_v, A.cols, dense, out, replicate=replicate if world > 1 else "nccl-broadcast")
+    if world > 1 and replicate != "nccl-broadcast":
+        dense.zero_()  # the full-size buffer is only a target now: what the product reads must come from the exchange
     result_h = torch.empty_like(out_h).pin_memory()
-    bcast = world > 1
+    ct = api._compute_type(d_v, out)
 
-    def step():
-        op.step(alpha, beta, broadcast=bcast)
+    # one GPU: the K products are issued by a compiled loop (include/b200sp_bench.h), as a C caller would
+    a_c, b_c = ctypes.c_float(alpha), ctypes.c_float(beta)
+    a_p, b_p = ctypes.cast(ctypes.byref(a_c), ctypes.c_void_p), ctypes.cast(ctypes.byref(b_c), ctypes.c_void_p)
+
+    def steps(count: int, with_exchange: bool):
+        if world == 1:
+            if is_spmm:
+                rc = L.b200spRepeatSpMM(op.handle.raw, 0, 0, a_p, op.A.raw, op.B.raw, b_p, op.C.raw, ct, 0,
+                                        api._ptr(op.buffer), count)
+            else:
+                rc = L.b200spRepeatSpMV(op.handle.raw, 0, a_p, op.A.raw, op.x.raw, b_p, op.y.raw, ct, 0,
+                                        api._ptr(op.buffer), count)
+            if rc != 0:
+                raise RuntimeError(f"compute entry point returned status {rc}")
+        else:
+            for _ in range(count):
+                op.step(alpha, beta, broadcast=with_exchange)
 
     def barrier():
         torch.cuda.synchronize()
@@ -364,21 +403,23 @@ def gpu_arm(args, synth, oracle):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    K, W = args.steps, args.warmup
-    for _ in range(W):
-        step()
+    # Set-up outside the timed region: the exchange (peer mappings or NCCL channels) is brought to its steady
+    # state with untimed steps on the real buffers, then the W warm-up steps the caller asked for.
+    settle = 30 if world > 1 else 0
+    steps(settle, True)
+    barrier()
+    steps(W, True)
     barrier()
 
     # ---- timed region: exactly K steps, inputs resident, CUDA events on the launching stream
-    sampler = ClockSampler(physical_gpu_index(local))
+    sampler = ClockSampler(physical_gpu_index(env.local))
     sampler.start()
-    count = pkg.lib().b200sp_kernel_launches
+    count = L.b200sp_kernel_launches
     count.restype = ctypes.c_ulonglong
     launches_before = count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(K):
-        step()
+    steps(K, True)
     e1.record()
     launches = int(count() - launches_before)  # this rank's kernels inside the timed region
     sampler.sample()
@@ -388,21 +429,34 @@ def gpu_arm(args, synth, oracle):
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = total_ms / K
 
-    # ---- compute-only steps (no broadcast): launch duration for the roofline.  A step is one
-    # launch of the dominant kernel (plus, for the binned SpMV, the long-row kernel running beside
-    # it on a side stream), so the duration is the event-bracketed region divided by the steps.
+    # ---- the same steps with an event after each, for the spread (an event costs a little: the mean above is
+    # the figure of record, these show whether it hides a transient)
+    KS = min(K, 200)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(KS + 1)]
+    barrier()
+    evs[0].record()
+    for i in range(KS):
+        steps(1, True)
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    per = np.array([evs[i].elapsed_time(evs[i + 1]) for i in range(KS)])
+    per_step = {"min": max_over_ranks(float(per.min())), "median": max_over_ranks(float(np.median(per))),
+                "max": max_over_ranks(float(per.max())), "steps": KS}
+
+    # ---- compute-only steps (no exchange): launch duration for the roofline.  A step is one launch of the
+    # dominant kernel (plus, where two run side by side, the one beside it), so the duration is the
+    # event-bracketed region divided by the steps.
     KL = min(K, 200)
     barrier()
     e0.record()
-    for _ in range(KL):
-        op.step(alpha, beta, broadcast=False)
+    steps(KL, False)
     e1.record()
     torch.cuda.synchronize()
     launch_ms_mean = max_over_ranks(e0.elapsed_time(e1) / KL)
+    exchange_error = op.replication_error()
 
-    # ---- end to end: host buffers in, host result out, every step.  The package's host-operand API cuts the
+    # ---- end to end: host buffers in, host result out, every step.  The package's host-operand call cuts the
     # rows into panels so that the copies of one panel overlap the product of another.
-    from ops_sparse_b200 import hostio
     KE = min(K, 200)
     pipe = hostio.HostOperandProduct(rp, d_ci, d_v, A.cols, dense, out, panels=args.e2e_panels)
     graph = pipe.capture(dense_h, out_h, result_h, alpha, beta) if (world == 1 and not args.no_graph) else None
@@ -411,7 +465,7 @@ def gpu_arm(args, synth, oracle):
         if graph is not None:
             graph.replay()  # the recorded step: x / B up, per panel y / C up -> product -> result down
         else:
-            pipe.step(dense_h, out_h, result_h, alpha, beta, upload_dense=(rank == 0))
+            pipe.step(dense_h, out_h, result_h, alpha, beta, upload_dense=True)
 
     for _ in range(3):
         e2e_step()
@@ -423,30 +477,37 @@ def gpu_arm(args, synth, oracle):
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / KE
+    del graph
     pipe.close()
-    # bytes this rank moves per step (rank 0 also uploads x / B; y / C goes up only when beta != 0 reads it)
     out_bytes = (r1 - r0) * n * out_h.element_size()
-    h2d = (dense_h.numel() * dense_h.element_size() if rank == 0 else 0) + (out_bytes if beta != 0 else 0)
+    h2d = dense_h.numel() * dense_h.element_size() + (out_bytes if beta != 0 else 0)
     d2h = out_bytes
 
-    # ---- spot check of the last end-to-end result against the CPU oracle (first local rows)
-    check_rows = min(r1 - r0, 20000 if not is_spmm else 512)
-    S = A.row_slice(r0, r0 + check_rows)
-    got = result_h[:check_rows].to(torch.float32).numpy().astype(np.float64)
-    if is_spmm:
-        Bw = dense_h.to(torch.float32).numpy()
-        C0 = out_h[:check_rows].to(torch.float32).numpy()
-        vw = torch.from_numpy(S.values).to(vt).to(torch.float32).numpy()
-        gold = oracle.spmm_f32(S.row_ptr, S.col_ind, vw, Bw, C0, alpha, beta)
-        scale = abs(alpha) * oracle.spmm_abs_sum(S.row_ptr, S.col_ind, vw, Bw) + np.abs(beta * C0)
-    else:
-        xw = dense_h.to(torch.float32).numpy()
-        y0 = out_h[:check_rows].to(torch.float32).numpy()
-        vw = torch.from_numpy(S.values).to(vt).to(torch.float32).numpy()
-        gold = oracle.spmv(S.row_ptr, S.col_ind, vw, xw, y0, alpha, beta)
-        scale = abs(alpha) * oracle.spmv_abs_rowsum(S.row_ptr, S.col_ind, vw, xw) + np.abs(beta * y0)
+    # ---- every output of the last end-to-end step against the CPU oracle (threaded, all local rows)
     tol = 1e-5 if cfg["val"] == "f32" else 2e-3
-    parity_ok = bool(np.all(np.abs(got - gold) <= tol * scale + 1e-30))
+    S = A.row_slice(r0, r1)
+    vw = torch.from_numpy(np.ascontiguousarray(S.values)).to(vt).to(torch.float32).numpy()
+    dw = dense_h.to(torch.float32).numpy()
+    ow = out_h.to(torch.float32).numpy()
+    gw = result_h.to(torch.float32).numpy()
+    t0 = time.perf_counter()
+    if is_spmm:
+        bad, worst = oracle.check_spmm_f32(S.row_ptr, S.col_ind, vw, dw, ow, gw, alpha, beta, tol)
+    else:
+        bad, worst = oracle.check_spmv_f32(S.row_ptr, S.col_ind, vw, dw, ow, gw, alpha, beta, tol)
+    check_s = time.perf_counter() - t0
+    del vw, dw, ow, gw
+    if world > 1:
+        t = torch.tensor([float(bad)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        bad = int(t.item())
+        t = torch.tensor([worst], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst = float(t.item())
+    parity = {"outputs_checked": int(A.rows * n), "outside_tolerance": int(bad), "worst_err_over_scale": worst,
+              "tolerance": tol, "rule": "|got - gold| <= tol * (|alpha| * sum |a b| + |beta * old|), every output",
+              "checker": "oracle/ (CPU golden restatement), all host threads", "seconds": round(check_s, 2),
+              "ok": bad == 0 and exchange_error == 0}
 
     alg_bytes, flops = bytes_and_flops(cfg, synth)
     my_bytes, _ = bytes_and_flops(cfg, synth, rows=r1 - r0, nnz=int(ci.size))
@@ -458,53 +519,91 @@ def gpu_arm(args, synth, oracle):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         base = cpu_baseline(cfg, oracle, oracle.hardware_threads())
 
-    if rank == 0:
-        line = {
-            "metric": metric_name(cfg), "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": dtype_name(cfg), "data": "synthetic (seeded)",
-            "config": describe(args.config, cfg) | {
-                "parallelism": f"rows split by nnz over {world} GPU(s); x/B broadcast from rank 0 inside every step"
-                if world > 1 else "single GPU",
-                "l2_policy": "no flush between steps: A (col_ind + values) alone is larger than L2 "
-                             f"({(4 + d_v.element_size()) * A.nnz / 1e6:.0f} MB vs 126 MB); x / B may stay cached"
-                if (4 + d_v.element_size()) * A.nnz > L2_BYTES else
-                "inputs fit in L2: this configuration is launch-latency bound, bandwidth fractions are not meaningful",
-                "analysis": "aclsparse*Preprocess once, outside the timed region",
-                "api": args.api,
-            },
-            "effective_gbs": alg_bytes / (ms_per_step * 1e-3) / 1e9,
-            "algorithmic_bytes_per_step": alg_bytes,
-            "roofline": {
-                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src,
-                "kernel": ("SpmvOpLongRowsKernel + SpmvOpRowsKernel per length class" if args.api == "spmvop-alg2"
-                           else "SpmvOpRowsKernel" if args.api == "spmvop-alg1"
-                           else dominant_kernels(is_spmm, launches / K, n * dense.element_size() if is_spmm else 0)),
-                "launch_ms_mean": launch_ms_mean,
-                "algorithmic_bytes_per_launch": my_bytes, "traffic": NCU_TRAFFIC_BYTES.get(args.config) if (world == 1 and args.api == "spmv") else None,
-                "note": BOUND_NOTES.get(args.config) if args.api == "spmv" else None,
-            },
-            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE,
-                    "row_panels": args.e2e_panels, "cuda_graph": graph is not None},
-            "compute_only": {"value": flops / (launch_ms_mean * 1e-3) / 1e9, "unit": "GFLOP/s",
-                             "ms_per_step": launch_ms_mean,
-                             "broadcast_ms_per_step": max(ms_per_step - launch_ms_mean, 0.0) if world > 1 else 0.0,
-                             "note": "max-over-ranks mean product time without the broadcast (an event after "
-                                     "every single step would add its own 15-30 us to a 95 us step, so no "
-                                     "per-step spread is reported)"},
-            "gpu_launches": launches * world, "kernels_per_step": launches / K, "clocks": clocks, "parity_spot_check": parity_ok,
-        }
-        if base is not None:
-            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "single_core")
-                                    if k in base}
-        print(json.dumps(line))
+    lps = launches / K
+    kernels = kernels_of(is_spmm, lps, n * dense.element_size() if is_spmm else 0, world)
+    traffic = NCU_TRAFFIC.get(name) if world == 1 else None
+    if traffic is not None and traffic["kernels"].split(" ")[0] not in kernels:
+        traffic = None
+    res = {
+        "metric": metric_name(cfg), "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_per_step, "per_step_ms": per_step, "dtype": dtype_name(cfg), "config": describe(cfg),
+        "effective_gbs": alg_bytes / (ms_per_step * 1e-3) / 1e9, "algorithmic_bytes_per_step": alg_bytes,
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src, "kernel": kernels,
+            "launch_ms_mean": launch_ms_mean, "algorithmic_bytes_per_launch": my_bytes,
+            "traffic": traffic["bytes"] if traffic else None, "traffic_source": traffic["source"] if traffic else None,
+            "note": BOUND_NOTES.get(name),
+        },
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE,
+                "row_panels": args.e2e_panels, "cuda_graph": world == 1 and not args.no_graph},
+        "compute_only": {"value": flops / (launch_ms_mean * 1e-3) / 1e9, "unit": "GFLOP/s",
+                         "ms_per_step": launch_ms_mean,
+                         "exchange_ms_per_step": max(ms_per_step - launch_ms_mean, 0.0) if world > 1 else 0.0},
+        "gpu_launches": launches * world, "kernels_per_step": lps, "clocks": clocks, "parity_full": parity,
+        "l2_policy": ("no flush between steps: A (col_ind + values) alone is larger than L2 "
+                      f"({(4 + d_v.element_size()) * A.nnz / 1e6:.0f} MB vs 126 MB); x / B may stay cached"
+                      if (4 + d_v.element_size()) * A.nnz > L2_BYTES else
+                      "inputs fit in L2: this configuration is launch-latency bound, bandwidth fractions are not "
+                      "meaningful"),
+    }
+    if base is not None:
+        res["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "single_core") if k in base}
     op.close()
-    if world > 1:
+    del op, dense, out, d_rp, d_ci, d_v, dense_h, out_h, result_h, cfg, A
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def gpu_arm(args, synth, oracle):
+    import torch
+    import torch.distributed as dist
+
+    env = Env()
+    env.world = int(os.environ.get("WORLD_SIZE", "1"))
+    env.rank = int(os.environ.get("RANK", "0"))
+    env.local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product path has no CPU implementation")
+    torch.cuda.set_device(env.local)
+    env.dev = torch.device("cuda", env.local)
+    if env.world > 1:
+        dist.init_process_group("nccl", device_id=env.dev)
+    env.torch, env.oracle, env.synth = torch, oracle, synth
+    env.pkg = entry.load_package()
+
+    names = config_list(args, env.world)
+    results = {}
+    for name in names:
+        results[name] = measure_config(name, args, env, head=(name == args.config))
+    if env.rank == 0:
+        h = results[args.config]
+        line = {
+            "metric": h["metric"], "value": h["value"], "unit": "GFLOP/s", "n_gpus": env.world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": h["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": h["dtype"], "data": "synthetic (seeded)", "config": h["config"],
+            "parallelism": ("single GPU" if env.world == 1 else
+                            f"rows split by nnz over {env.world} GPUs; x / B held in {env.world} slices and replicated "
+                            f"inside every step ({args.replicate}); 30 untimed steps before the warm-up bring the "
+                            "exchange to its steady state"),
+            "analysis": "aclsparse*Preprocess once, outside the timed region",
+            "step_issue": ("compiled loop over the C API (b200spRepeatSpMV / b200spRepeatSpMM)" if env.world == 1
+                           else "Python loop: one exchange launch and one aclsparse call per step"),
+        }
+        for k in ("per_step_ms", "effective_gbs", "algorithmic_bytes_per_step", "roofline", "e2e", "compute_only",
+                  "gpu_launches", "kernels_per_step", "clocks", "parity_full", "l2_policy", "cpu_baseline"):
+            if k in h:
+                line[k] = h[k]
+        line["configs"] = results
+        print(json.dumps(line))
+    if env.world > 1:
+        dist.barrier()
         dist.destroy_process_group()
-    if not parity_ok:
-        raise SystemExit("parity spot check against the CPU oracle failed")
+    bad = [n for n, r in results.items() if not r["parity_full"]["ok"]]
+    if bad:
+        raise SystemExit(f"parity check against the CPU oracle failed for {bad}")
 
 
 def main():
@@ -513,22 +612,26 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--config", default="c2", choices=list(ALL_CONFIGS), help="the headline configuration")
+    ap.add_argument("--configs", default="", help="comma-separated configurations to measure (default: all five on "
+                                                  "one GPU, c2 and c5 on several); the headline is always included")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU golden timing leg")
-    ap.add_argument("--api", default="spmv", choices=["spmv", "spmvop-alg1", "spmvop-alg2"],
-                    help="resident-operand legs through aclsparseSpMV (default) or the SpMVOp plan API")
+    ap.add_argument("--replicate", default="peer", choices=["peer", "nccl-allgather", "nccl-broadcast"],
+                    help="how x / B reaches every GPU inside a multi-GPU step (see ops-sparse_b200/mg.py)")
     ap.add_argument("--no-graph", action="store_true", help="end-to-end leg: issue every step's operations one by one")
     ap.add_argument("--e2e-panels", type=int, default=4,
                     help="row panels the end-to-end leg pipelines its host copies over (1 = copy, compute, copy)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    entry.load_package()
-    from ops_sparse_b200 import synth
     entry._load("b200sp_build_oracle", ROOT / "oracle" / "build_oracle.py").build_oracle()
     oracle = entry.load_oracle()
     if args.impl == "reference":
+        # the CPU arm never maps the CUDA library: the workload generator is loaded on its own
+        synth = entry._load("b200sp_synth", ROOT / "ops-sparse_b200" / "synth.py")
         reference_arm(args, synth, oracle)
     else:
+        entry.load_package()
+        from ops_sparse_b200 import synth
         gpu_arm(args, synth, oracle)
 
 

@@ -101,6 +101,8 @@ _SIGNATURES = {
     "aclsparseSpMVGetBufferSize": [P, c_int, P, P, P, P, P, c_int, c_int, POINTER(c_size_t)],
     "aclsparseSpMVPreprocess": [P, c_int, P, P, P, P, P, c_int, c_int, P],
     "aclsparseSpMV": [P, c_int, P, P, P, P, P, c_int, c_int, P],
+    "b200spRepeatSpMV": [P, c_int, P, P, P, P, P, c_int, c_int, P, c_int],
+    "b200spRepeatSpMM": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P, c_int],
     # SpMM: handle, opA, opB, alpha, matA, matB, beta, matC, computeType, alg, (size* | buffer)
     "aclsparseSpMMGetBufferSize": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, POINTER(c_size_t)],
     "aclsparseSpMMPreprocess": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P],

@@ -24,6 +24,7 @@ LIB_PATH = LIB_DIR / "libops_sparse.so"
 SOURCES = [
     "common/context.cpp",
     "common/descr.cpp",
+    "common/repeat.cpp",
     "spmv/spmv_host.cpp",
     "spmv/spmv_kernels.cu",
     "spmv_op/spmv_op_host.cpp",
@@ -35,6 +36,7 @@ SOURCES = [
     "spmm/spmm_host.cpp",
     "spmm/spmm_kernels.cu",
     "mg/partition.cpp",
+    "mg/exchange.cu",
 ]
 
 NVCC_FLAGS = [

@@ -53,7 +53,6 @@ class HostOperandProduct:
         self.cuts = aligned_cuts(np.ascontiguousarray(row_ptr, dtype=np.int32), panels)
         self.streams = [torch.cuda.Stream(device=dense.device) for _ in range(max(1, min(streams, panels)))]
         self.dense_ready = torch.cuda.Event()
-        self.old, self.upload, self.old_ready = None, None, None  # created by the first step that needs them
         self.ops = []
         dev = dense.device
         for p in range(panels):
@@ -70,46 +69,29 @@ class HostOperandProduct:
         torch.cuda.synchronize(dev)
 
     def step(self, dense_h: torch.Tensor, out_h: torch.Tensor, result_h: torch.Tensor, alpha: float, beta: float,
-             upload_dense: bool = True) -> None:
-        """Enqueues one product; `result_h` holds it once every panel stream (or the device) is synchronised."""
+             upload_dense: bool = True, broadcast: bool = False) -> None:
+        """Enqueues one product; `result_h` holds it once every panel stream (or the device) is synchronised.
+        In a multi-rank job every rank uploads x / B from its own host copy (upload_dense on all ranks), or one
+        rank uploads and `broadcast` replicates it from rank `src`."""
         main = torch.cuda.current_stream()
         if upload_dense:
             self.dense.copy_(dense_h, non_blocking=True)
-        mg.broadcast_(self.dense, self.src, self.group)
+        if broadcast:
+            mg.broadcast_(self.dense, self.src, self.group)
         self.dense_ready.record(main)
-        # fp32 results: the old y / C need not be on the device before the product starts.  It travels on
-        # its own stream while alpha * A * x is computed (beta = 0 call), and beta * old is added afterwards
-        # by one fused multiply-add per element -- the same final operation, on the same fp32 operands.
-        late_old = beta != 0.0 and self.out.dtype == torch.float32
-        if late_old:
-            if self.old is None:
-                self.old = torch.empty_like(self.out)
-                self.upload = torch.cuda.Stream(device=self.out.device)
-                self.old_ready = [torch.cuda.Event() for _ in self.ops]
-            self.upload.wait_event(self.dense_ready)  # behind x / B on the host-to-device engine
-            with torch.cuda.stream(self.upload):
-                for i, (r0, r1, _, _) in enumerate(self.ops):
-                    if r1 > r0:
-                        self.old[r0:r1].copy_(out_h[r0:r1], non_blocking=True)
-                    self.old_ready[i].record(self.upload)
         for i, (r0, r1, s, op) in enumerate(self.ops):
             if r1 == r0:
                 continue
             s.wait_event(self.dense_ready)
             with torch.cuda.stream(s):
-                if late_old:
-                    op.step(alpha, 0.0, broadcast=False)
-                    s.wait_event(self.old_ready[i])
-                    self.out[r0:r1].add_(self.old[r0:r1], alpha=beta)
-                else:
-                    if beta != 0.0:
-                        self.out[r0:r1].copy_(out_h[r0:r1], non_blocking=True)
-                    op.step(alpha, beta, broadcast=False)
+                # beta * old is applied by the product kernel's own epilogue, so the old rows of this panel go
+                # up first; the copy of panel p + 1 overlaps the product of panel p on another stream.
+                if beta != 0.0:
+                    self.out[r0:r1].copy_(out_h[r0:r1], non_blocking=True)
+                op.step(alpha, beta, broadcast=False)
                 result_h[r0:r1].copy_(self.out[r0:r1], non_blocking=True)
         for s in self.streams:
             main.wait_stream(s)
-        if late_old:
-            main.wait_stream(self.upload)
 
     def capture(self, dense_h: torch.Tensor, out_h: torch.Tensor, result_h: torch.Tensor, alpha: float, beta: float,
                 upload_dense: bool = True) -> "torch.cuda.CUDAGraph":

@@ -87,6 +87,18 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
             else torch.zeros(A.cols, 8)
         mg.broadcast_(B, src=0)
         C_local = oracle.spmm_f32(rp, ci, v, B.numpy(), np.zeros((r1 - r0, 8), np.float32), 1.0, 0.0)
+        # all-gather form: x is held in slices, one per rank (slice_cuts), and gathered into a full copy
+        xc = mg.slice_cuts(A.cols, world, 4)
+        assert xc[0] == 0 and xc[-1] == A.cols
+        mine = torch.from_numpy(c["x"][int(xc[rank]):int(xc[rank + 1])].copy())
+        gathered = torch.full((A.cols,), float("nan"))
+        if len(set(np.diff(xc).tolist())) == 1:
+            dist.all_gather_into_tensor(gathered, mine)
+        else:
+            parts = [torch.empty(int(xc[g + 1] - xc[g])) for g in range(world)]
+            dist.all_gather(parts, mine)
+            gathered = torch.cat(parts)
+        assert np.array_equal(gathered.numpy(), c["x"])
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), y=y_local, C=C_local, rows=np.array([r0, r1]))
         dist.barrier()
     finally:
@@ -108,3 +120,15 @@ def test_two_ranks_gloo(pkg, oracle, tmp_path):
     assert got[0]["rows"][0] == 0 and got[0]["rows"][1] == got[1]["rows"][0] and got[1]["rows"][1] == A.rows
     assert np.array_equal(np.concatenate([g["y"] for g in got]), full_y)
     assert np.array_equal(np.concatenate([g["C"] for g in got]), full_C)
+
+
+def test_slice_cuts(pkg):
+    from ops_sparse_b200 import mg
+    for n, parts, align in ((1 << 20, 8, 4), (1000, 3, 4), (10, 3, 4), (7, 8, 1), (0, 4, 4), (2097152, 8, 1)):
+        cuts = mg.slice_cuts(n, parts, align)
+        assert cuts.size == parts + 1 and cuts[0] == 0 and cuts[-1] == n and np.all(np.diff(cuts) >= 0)
+        assert np.all(cuts[:-1] % align == 0)  # every slice starts on the alignment the push kernel needs
+        if n >= parts * align:
+            assert np.diff(cuts).max() - np.diff(cuts).min() <= 2 * align
+    with pytest.raises(ValueError):
+        mg.slice_cuts(10, 0)
