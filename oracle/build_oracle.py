@@ -3,9 +3,13 @@
   oracle/_build/liboracle.so      the CPU restatement (oracle.cpp), always built
   oracle/_ref/libref_*.so         the reference's own golden functions, compiled from the
                                   reference checkout where it lies (only when it is present)
+  oracle/_ref/libref_{convert,sddmm}.so
+                                  the reference's golden headers for the CSR producers and SDDMM, likewise
   oracle/_ref/{spmv,spmm35,spmm22}_test
                                   the reference's own harness programs, unmodified, linked
                                   against libops_sparse.so through the acl->CUDA shim headers
+The reference checkout is looked for at $B200SP_REFERENCE_DIR, else in a `reference` directory beside this
+repository.
 
 Nothing built here is part of the shipped library.  `python oracle/build_oracle.py [--force]`.
 """
@@ -21,13 +25,25 @@ ROOT = HERE.parent
 BUILD = HERE / "_build"
 REFOUT = HERE / "_ref"
 ORACLE_LIB = BUILD / "liboracle.so"
-REFERENCE = Path(os.environ.get("B200SP_REFERENCE_DIR", "/root/reference"))
+# Where the reference checkout lies: B200SP_REFERENCE_DIR, or a `reference` directory beside this repository.
+REFERENCE = Path(os.environ.get("B200SP_REFERENCE_DIR", str(ROOT.parent / "reference")))
 CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 
 REF_UNITS = {
     "spmv": ("test/spmv/arch22/spmv_test.cpp", "ref_wrap_spmv.cpp"),
     "spmm35": ("test/spmm/arch35/spmm_test.cpp", "ref_wrap_spmm35.cpp"),
     "spmm22": ("test/spmm/arch22/spmm_test.cpp", "ref_wrap_spmm22.cpp"),
+}
+
+
+# Golden headers of the operators next to the hot path (CSR producers, SDDMM): header-only, wrapped as libraries.
+REF_HEADER_UNITS = {
+    "convert": ("ref_wrap_convert.cpp", {
+        "REF_CSRSORT_GOLDEN": "test/csrsort/arch35/csrsort_golden.h",
+        "REF_COO2CSR_GOLDEN": "test/coo2csr/coo2csr_golden.h",
+        "REF_CSR2CSC_GOLDEN": "test/csr2csc_ex2/csr2csc_ex2_golden.h",
+    }),
+    "sddmm": ("ref_wrap_sddmm.cpp", {"REF_SDDMM_GOLDEN": "test/sddmm/sddmm/sddmm_golden.h"}),
 }
 
 
@@ -77,6 +93,16 @@ def build_reference(force: bool = False, ops_lib: Path | None = None) -> dict[st
             _run([*common, str(ref_src), "-o", str(exe), *link])
         out[f"lib_{name}"] = lib
         out[f"exe_{name}"] = exe
+    frame = ["-I", str(REFERENCE / "test" / "frame")]
+    for name, (wrap, headers) in REF_HEADER_UNITS.items():
+        srcs = [REFERENCE / rel for rel in headers.values()]
+        if not all(p.exists() for p in srcs):
+            continue
+        lib = REFOUT / f"libref_{name}.so"
+        if force or not _newer(lib, HERE / wrap, *srcs):
+            defs = [f'-D{macro}="{REFERENCE / rel}"' for macro, rel in headers.items()]
+            _run([*common, *frame, "-fPIC", "-shared", *defs, str(HERE / wrap), "-o", str(lib)])
+        out[f"lib_{name}"] = lib
     return out
 
 

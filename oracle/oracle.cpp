@@ -383,6 +383,133 @@ void oracle_spmm_abs_sum(const int32_t *row_ptr, const int32_t *col_ind, const v
     }
 }
 
+// ---- CSR producers (integer work: results must match the reference's goldens bit for bit) ----------
+
+// aclsparseXcsrsort: inside every row the column indices are put in ascending order, equal columns keep their
+// input order, and the permutation array travels with them (csrsortGolden, test/csrsort/arch35/
+// csrsort_golden.h:38-70).  row_ptr is in `index_base`.
+void oracle_csrsort(const int32_t *row_ptr, const int32_t *col_ind, const int32_t *perm, int m, int index_base,
+                    int32_t *col_out, int32_t *perm_out)
+{
+    std::vector<int32_t> order;
+    for (int r = 0; r < m; ++r) {
+        const int lo = row_ptr[r] - index_base, hi = row_ptr[r + 1] - index_base;
+        order.resize((size_t)std::max(hi - lo, 0));
+        for (int i = 0; i < hi - lo; ++i) order[(size_t)i] = lo + i;
+        std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return col_ind[a] < col_ind[b]; });
+        for (int i = 0; i < hi - lo; ++i) {
+            col_out[lo + i] = col_ind[order[(size_t)i]];
+            perm_out[lo + i] = perm[order[(size_t)i]];
+        }
+    }
+}
+
+// aclsparseXcoo2csr: row pointers from sorted COO row indices by counting and a running sum; indices outside
+// [0, m) after removing the base are ignored (Coo2CsrGolden, test/coo2csr/coo2csr_golden.h:44-77).
+void oracle_coo2csr(const int32_t *coo_row, int nnz, int m, int index_base, int32_t *row_ptr)
+{
+    for (int i = 0; i <= m; ++i) row_ptr[i] = index_base;
+    if (nnz <= 0 || m <= 0) return;
+    std::vector<int64_t> count((size_t)m, 0);
+    for (int k = 0; k < nnz; ++k) {
+        const int r = (int)((uint32_t)coo_row[k] - (uint32_t)index_base);
+        if (r >= 0 && r < m) ++count[(size_t)r];
+    }
+    int64_t running = 0;
+    for (int i = 0; i < m; ++i) {
+        running += count[(size_t)i];
+        row_ptr[i + 1] = (int32_t)(running + index_base);
+    }
+}
+
+// aclsparseCsr2cscEx2: column counts, exclusive scan, then every entry is dropped into its column in row order,
+// values moved as raw bytes (Csr2CscGolden, test/csr2csc_ex2/csr2csc_ex2_golden.h:50-110).
+void oracle_csr2csc(int m, int n, int nnz, const int32_t *row_ptr, const int32_t *col_ind, const void *values,
+                    int value_bytes, int index_base, int32_t *col_ptr, int32_t *row_ind, void *val_out)
+{
+    for (int j = 0; j <= n; ++j) col_ptr[j] = index_base;
+    if (nnz <= 0) return;
+    std::vector<int32_t> next((size_t)n, 0);
+    for (int k = 0; k < nnz; ++k) ++next[(size_t)(col_ind[k] - index_base)];
+    int32_t running = 0;
+    for (int j = 0; j < n; ++j) {
+        const int32_t c = next[(size_t)j];
+        next[(size_t)j] = running;
+        running += c;
+        col_ptr[j + 1] = running + index_base;
+    }
+    const unsigned char *src = static_cast<const unsigned char *>(values);
+    unsigned char *dst = static_cast<unsigned char *>(val_out);
+    for (int r = 0; r < m; ++r) {
+        for (int k = row_ptr[r] - index_base; k < row_ptr[r + 1] - index_base; ++k) {
+            const int32_t where = next[(size_t)(col_ind[k] - index_base)]++;
+            row_ind[where] = r + index_base;
+            if (src != nullptr && dst != nullptr)
+                std::memcpy(dst + (size_t)where * (size_t)value_bytes, src + (size_t)k * (size_t)value_bytes,
+                            (size_t)value_bytes);
+        }
+    }
+}
+
+// ---- SDDMM: out[p] = alpha * <op(X) row i, op(Y) column j> + beta * c_init[p] in fp64 on the pattern of C
+// (SddmmGolden, test/sddmm/sddmm/sddmm_golden.h:106-150).  X is m x k (or k x m when transposed), Y is k x n (or
+// n x k when transposed), both row-major and compact. ---------------------------------------------------
+void oracle_sddmm_f64(int64_t m, int64_t n, int64_t k, const double *X, const double *Y, const int32_t *row_offsets,
+                      const int32_t *col_ind, const double *c_init, double alpha, double beta, int op_x_t, int op_y_t,
+                      double *out)
+{
+    for (int64_t i = 0; i < m; ++i) {
+        for (int32_t p = row_offsets[i]; p < row_offsets[i + 1]; ++p) {
+            const int64_t j = col_ind[p];
+            double dot = 0.0;
+            for (int64_t t = 0; t < k; ++t) {
+                const double xv = op_x_t ? X[t * m + i] : X[i * k + t];
+                const double yv = op_y_t ? Y[j * k + t] : Y[t * n + j];
+                dot += xv * yv;
+            }
+            out[p] = alpha * dot + beta * c_init[p];
+        }
+    }
+}
+
+// Mixed tolerance of the reference's test frame (test/frame/verify.h:193-300): an element fails when
+// |out - gold| > atol + rtol * |gold|; the case passes when at least `ratio` of the elements do not fail and no
+// element is further from its golden than max(limit, 32 ulp of the golden in the output type) or is NaN / inf.
+// Returns 1 on pass; stats = {matched ratio, max abs error}.
+int oracle_verify_mixed_tolerance(const float *out, const float *gold, int64_t count, double rtol, double atol,
+                                  double limit, int mantissa_bits, int emin, double ratio, double *stats)
+{
+    int64_t failed = 0;
+    bool beyond = false;
+    double worst = 0.0;
+    for (int64_t i = 0; i < count; ++i) {
+        const float o = out[i], g = gold[i];
+        if (std::isnan(o) || std::isnan(g) || std::isinf(o) || std::isinf(g)) {
+            beyond = true;
+            ++failed;
+            continue;
+        }
+        const double diff = std::fabs((double)o - (double)g), mag = std::fabs((double)g);
+        worst = std::max(worst, diff);
+        double ulp;
+        if (mag == 0.0) {
+            ulp = std::pow(2.0, (double)(emin - mantissa_bits));
+        } else {
+            int e = 0;
+            std::frexp(mag, &e);
+            ulp = std::ldexp(1.0, std::max(e - 1, emin) - mantissa_bits);
+        }
+        if (diff > atol + rtol * mag) ++failed;
+        if (diff > std::max(limit, 32.0 * ulp)) beyond = true;
+    }
+    const double matched = count > 0 ? (double)(count - failed) / (double)count : 1.0;
+    if (stats != nullptr) {
+        stats[0] = matched;
+        stats[1] = worst;
+    }
+    return (matched >= ratio && !beyond) ? 1 : 0;
+}
+
 // ---- whole-result checks at benchmark size -------------------------------------------------
 // The per-row tolerance of the benchmark, |got - gold| <= tol * (|alpha| * sum_j |a_ij * b_j| + |beta * old|),
 // applied to EVERY output of a full-size product without materialising golden or scale arrays (config 5 has

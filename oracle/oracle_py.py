@@ -189,6 +189,59 @@ def spmm_abs_sum(row_ptr, col_ind, val, B, val_type="f32") -> np.ndarray:
     return out
 
 
+# ---- CSR producers and SDDMM -------------------------------------------------------------------------
+
+def csrsort(row_ptr, col_ind, perm, index_base=0):
+    """(sorted col_ind, permuted perm): golden of aclsparseXcsrsort."""
+    row_ptr, col_ind, perm = _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(perm, np.int32)
+    co, po = col_ind.copy(), perm.copy()
+    lib().oracle_csrsort(_p(row_ptr), _p(col_ind), _p(perm), int(row_ptr.size - 1), int(index_base), _p(co), _p(po))
+    return co, po
+
+
+def coo2csr(coo_row, m, index_base=0):
+    coo_row = _c(coo_row, np.int32)
+    out = np.empty(m + 1, dtype=np.int32)
+    lib().oracle_coo2csr(_p(coo_row), int(coo_row.size), int(m), int(index_base), _p(out))
+    return out
+
+
+def csr2csc(m, n, row_ptr, col_ind, values, index_base=0):
+    """(col_ptr, row_ind, values in CSC order); values of any 1-, 2- or 4-byte dtype move as raw bytes."""
+    row_ptr, col_ind = _c(row_ptr, np.int32), _c(col_ind, np.int32)
+    values = np.ascontiguousarray(values)
+    cp, ri, vo = np.empty(n + 1, dtype=np.int32), np.empty(col_ind.size, dtype=np.int32), np.empty_like(values)
+    lib().oracle_csr2csc(int(m), int(n), int(col_ind.size), _p(row_ptr), _p(col_ind), _p(values),
+                         int(values.dtype.itemsize), int(index_base), _p(cp), _p(ri), _p(vo))
+    return cp, ri, vo
+
+
+def sddmm_f64(m, n, k, X, Y, row_offsets, col_ind, c_init, alpha, beta, op_x_t=False, op_y_t=False):
+    X, Y, c_init = _c(X, np.float64).ravel(), _c(Y, np.float64).ravel(), _c(c_init, np.float64)
+    row_offsets, col_ind = _c(row_offsets, np.int32), _c(col_ind, np.int32)
+    out = np.zeros(col_ind.size, dtype=np.float64)
+    lib().oracle_sddmm_f64(c_int64(m), c_int64(n), c_int64(k), _p(X), _p(Y), _p(row_offsets), _p(col_ind),
+                           _p(c_init), c_double(alpha), c_double(beta), int(op_x_t), int(op_y_t), _p(out))
+    return out
+
+
+FRAME_MIXED_TOL = {  # rtol, atol, fixed per-element limit, mantissa bits, emin (test/frame/verify.h:214-226)
+    "f16": (0.001953125, 0.001953125, 1e-1, 10, -14),
+    "bf16": (0.015625, 0.015625, 1.0, 7, -126),
+    "f32": (0.0009765625, 1.52587890625e-5, 1e-2, 23, -126),
+}
+
+
+def verify_mixed_tolerance(out, gold, kind="f32"):
+    """The reference test frame's MIXED_TOLERANCE verdict: (passed, {matched, max_abs_err})."""
+    rtol, atol, limit, mant, emin = FRAME_MIXED_TOL[kind]
+    out, gold = _c(out, np.float32).ravel(), _c(gold, np.float32).ravel()
+    stats = np.zeros(2, dtype=np.float64)
+    ok = lib().oracle_verify_mixed_tolerance(_p(out), _p(gold), c_int64(out.size), c_double(rtol), c_double(atol),
+                                             c_double(limit), int(mant), int(emin), c_double(0.99), _p(stats))
+    return ok == 1, {"matched": float(stats[0]), "max_abs_err": float(stats[1])}
+
+
 # ---- whole-result checks at benchmark size --------------------------------------------------------
 
 def check_spmv_f32(row_ptr, col_ind, val, x, y_old, got, alpha, beta, tol, threads=None):
@@ -419,3 +472,75 @@ def time_spmm_f32(row_ptr, col_ind, val, B, C, alpha, beta, threads: int, reps: 
         spmm_f32(row_ptr, col_ind, val, B, C, alpha, beta, threads=threads)
         per[r] = time.perf_counter() - t0
     return per[:reps], "port"
+
+
+def ref_csrsort(row_ptr, col_ind, perm, index_base=0):
+    row_ptr, col_ind, perm = _c(row_ptr, np.int32), _c(col_ind, np.int32), _c(perm, np.int32)
+    co, po = np.empty_like(col_ind), np.empty_like(perm)
+    ref_lib("convert").ref_csrsort(_p(row_ptr), _p(col_ind), _p(perm), int(row_ptr.size - 1), int(col_ind.size),
+                                   int(index_base), _p(co), _p(po))
+    return co, po
+
+
+def ref_coo2csr(coo_row, m, index_base=0):
+    coo_row = _c(coo_row, np.int32)
+    out = np.empty(m + 1, dtype=np.int32)
+    rc = ref_lib("convert").ref_coo2csr(_p(coo_row), int(coo_row.size), int(m), int(index_base), _p(out))
+    assert rc == 0
+    return out
+
+
+def ref_csr2csc(m, n, row_ptr, col_ind, values, index_base=0):
+    row_ptr, col_ind = _c(row_ptr, np.int32), _c(col_ind, np.int32)
+    values = np.ascontiguousarray(values)
+    cp, ri, vo = np.empty(n + 1, dtype=np.int32), np.empty(col_ind.size, dtype=np.int32), np.empty_like(values)
+    rc = ref_lib("convert").ref_csr2csc(int(m), int(n), int(col_ind.size), _p(row_ptr), _p(col_ind), _p(values),
+                                        int(values.dtype.itemsize), int(index_base), _p(cp), _p(ri), _p(vo))
+    assert rc == 0
+    return cp, ri, vo
+
+
+def ref_sddmm_f64(m, n, k, X, Y, row_offsets, col_ind, c_init, alpha, beta, op_x_t=False, op_y_t=False):
+    X, Y, c_init = _c(X, np.float64).ravel(), _c(Y, np.float64).ravel(), _c(c_init, np.float64)
+    row_offsets, col_ind = _c(row_offsets, np.int32), _c(col_ind, np.int32)
+    out = np.zeros(col_ind.size, dtype=np.float64)
+    ref_lib("sddmm").ref_sddmm_f64(c_int64(m), c_int64(n), c_int64(k), _p(X), c_int64(X.size), _p(Y), c_int64(Y.size),
+                                   _p(row_offsets), _p(col_ind), _p(c_init), c_int64(col_ind.size), c_double(alpha),
+                                   c_double(beta), int(op_x_t), int(op_y_t), _p(out))
+    return out
+
+
+def ref_sddmm_sparsity(m, n, ratio, lo, hi, seed):
+    """(row_offsets, col_ind, fp64 values) of the reference's deterministic SDDMM pattern generator."""
+    f = ref_lib("sddmm").ref_sddmm_sparsity
+    f.restype = c_int64
+    nnz = f(c_int64(m), c_int64(n), c_double(ratio), c_double(lo), c_double(hi), c_uint32(seed), None, None, None)
+    ro, ci, v = np.zeros(m + 1, np.int32), np.zeros(nnz, np.int32), np.zeros(nnz, np.float64)
+    f(c_int64(m), c_int64(n), c_double(ratio), c_double(lo), c_double(hi), c_uint32(seed), _p(ro), _p(ci), _p(v))
+    return ro, ci, v
+
+
+def ref_sddmm_f32_to_f16(a):
+    a = _c(a, np.float32).ravel()
+    out = np.empty(a.size, dtype=np.uint16)
+    ref_lib("sddmm").ref_sddmm_f32_to_f16(_p(a), _p(out), c_int64(a.size))
+    return out
+
+
+def ref_sddmm_f16_to_f32(a):
+    a = _c(a, np.uint16).ravel()
+    out = np.empty(a.size, dtype=np.float32)
+    ref_lib("sddmm").ref_sddmm_f16_to_f32(_p(a), _p(out), c_int64(a.size))
+    return out
+
+
+def ref_verify_mixed_tolerance(out, gold, kind="f32") -> bool:
+    out, gold = _c(out, np.float32).ravel(), _c(gold, np.float32).ravel()
+    dtype = {"f32": 0, "f16": 1, "bf16": 27}[kind]
+    return ref_lib("sddmm").ref_verify_mixed_tolerance(_p(out), _p(gold), c_int64(out.size), dtype) == 1
+
+
+def ref_sddmm_uniform(seed, lo, hi, n):
+    out = np.empty(n, dtype=np.float64)
+    ref_lib("sddmm").ref_sddmm_uniform(c_uint32(seed), c_double(lo), c_double(hi), c_int64(n), _p(out))
+    return out

@@ -14,6 +14,11 @@ Fixture contents (all small):
   spmv.npz          SpmvCpu / SpmvTransCpu on seeded inputs for all seven type triples (the
                     harness itself is time-seeded, so only its functions are pinned, on inputs
                     drawn here with its distributions: values, x, y ~ U(-5, 5))
+  convert.npz       csrsortGolden / Coo2CsrGolden / Csr2CscGolden (test/csrsort/arch35/csrsort_golden.h,
+                    test/coo2csr/coo2csr_golden.h, test/csr2csc_ex2/csr2csc_ex2_golden.h) on seeded index
+                    arrays, both index bases, duplicates and empty rows included
+  sddmm.npz         a slice of the reference's SDDMM case table (test/sddmm/sddmm/arch35/sddmm_test.csv) with
+                    its pattern generator, its seeds for X / Y / C and SddmmGolden's fp64 results
 """
 from __future__ import annotations
 
@@ -155,6 +160,79 @@ def spmv():
     np.savez_compressed(OUT / "spmv.npz", **out)
 
 
+def convert():
+    rng = np.random.default_rng(2026)
+    out = {}
+    sort_cases = [("tiny", 1, 1, 1.0, False), ("dups", 50, 40, 12.0, True), ("wide", 100, 5000, 30.0, False),
+                  ("long", 6, 100000, 1500.0, False), ("many_short", 800, 300, 4.0, True), ("empty", 64, 64, 0.0, False)]
+    out["sort_names"] = np.array([c[0] for c in sort_cases])
+    for name, m, n, mean_len, dups in sort_cases:
+        lengths = rng.poisson(mean_len, size=m).astype(np.int64) if mean_len else np.zeros(m, np.int64)
+        if not dups:
+            lengths = np.minimum(lengths, n)
+        rp = np.zeros(m + 1, np.int32)
+        rp[1:] = np.cumsum(lengths)
+        cols = [rng.integers(0, n, size=int(k)) if dups else rng.permutation(n)[:int(k)] for k in lengths]
+        ci = (np.concatenate(cols) if rp[-1] else np.zeros(0)).astype(np.int32)
+        for base in (0, 1):
+            perm = np.arange(ci.size, dtype=np.int32)
+            co, po = o.ref_csrsort(rp + base, ci + base, perm, base)
+            out[f"sort/{name}/{base}/row_ptr"], out[f"sort/{name}/{base}/col_ind"] = rp + base, ci + base
+            out[f"sort/{name}/{base}/col_out"], out[f"sort/{name}/{base}/perm_out"] = co, po
+            out[f"sort/{name}/{base}/n"] = np.array([n])
+    coo_cases = [("one", 1, 1, 0.0), ("small", 7, 30, 0.0), ("half_empty", 1000, 5000, 0.5), ("no_entries", 4096, 0, 0.0),
+                 ("no_rows", 0, 0, 0.0)]
+    out["coo_names"] = np.array([c[0] for c in coo_cases])
+    for name, m, nnz, empty in coo_cases:
+        live = np.flatnonzero(rng.random(m) >= empty) if m else np.zeros(0, np.int64)
+        rows = np.sort(rng.choice(live, size=nnz)) if (nnz and live.size) else np.zeros(0, np.int64)
+        for base in (0, 1):
+            r = (rows + base).astype(np.int32)
+            out[f"coo/{name}/{base}/rows"], out[f"coo/{name}/{base}/m"] = r, np.array([m])
+            out[f"coo/{name}/{base}/row_ptr"] = o.ref_coo2csr(r, m, base)
+    csc_cases = [("square", 300, 300, 9.0), ("tall", 800, 50, 3.0), ("flat", 20, 6000, 150.0), ("empty", 10, 12, 0.0)]
+    out["csc_names"] = np.array([c[0] for c in csc_cases])
+    for name, m, n, mean_len in csc_cases:
+        lengths = np.minimum(rng.poisson(mean_len, size=m), n).astype(np.int64) if mean_len else np.zeros(m, np.int64)
+        rp = np.zeros(m + 1, np.int32)
+        rp[1:] = np.cumsum(lengths)
+        ci = (np.concatenate([np.sort(rng.permutation(n)[:int(k)]) for k in lengths]) if rp[-1] else np.zeros(0)).astype(np.int32)
+        vals = rng.integers(0, 1 << 31, size=ci.size).astype(np.uint32)
+        for base in (0, 1):
+            cp, ri, vo = o.ref_csr2csc(m, n, rp + base, ci + base, vals, base)
+            out[f"csc/{name}/{base}/shape"] = np.array([m, n])
+            out[f"csc/{name}/{base}/row_ptr"], out[f"csc/{name}/{base}/col_ind"], out[f"csc/{name}/{base}/val"] = rp + base, ci + base, vals
+            out[f"csc/{name}/{base}/col_ptr"], out[f"csc/{name}/{base}/row_ind"], out[f"csc/{name}/{base}/val_out"] = cp, ri, vo
+    np.savez_compressed(OUT / "convert.npz", **out)
+
+
+def sddmm():
+    # name, m, k, n, ratio, alpha, beta, dtype, lo, hi, seed: rows of the reference's case table (op_x = N, op_y = T,
+    # row-major operands, as in every row of that table)
+    cases = [("L0_01", 128, 64, 128, 0.5, 1.0, 0.0, "f32", -1.0, 1.0, 1), ("L0_02", 64, 32, 64, 0.5, 1.0, 0.0, "f16", -0.5, 0.5, 6),
+             ("L1_08", 100, 50, 100, 0.5, -1.0, 0.0, "f32", -1.0, 1.0, 13), ("L1_11", 48, 24, 48, 0.5, 1.0, 1.0, "f32", -1.0, 1.0, 17),
+             ("L2_07", 64, 32, 64, 0.0, 1.0, 0.0, "f32", -1.0, 1.0, 21), ("WB_02", 1, 32, 64, 0.5, 1.0, 0.0, "f16", -0.5, 0.5, 23),
+             ("WB_05", 64, 1, 64, 0.5, 1.0, 0.0, "f32", -1.0, 1.0, 26), ("WB_07", 1, 64, 100, 1.0, 1.0, 1.0, "f32", -1.0, 1.0, 28),
+             ("WB_08", 16, 64, 16, 0.5, 2.0, 0.0, "f16", -50.0, 50.0, 29)]
+    out = {"names": np.array([c[0] for c in cases])}
+    for name, m, k, n, ratio, alpha, beta, dtype, lo, hi, seed in cases:
+        ro, ci, cv = o.ref_sddmm_sparsity(m, n, ratio, lo, hi, seed)
+        X = o.ref_sddmm_uniform(seed + 1, lo, hi, m * k)          # m x k row-major
+        Yt = o.ref_sddmm_uniform(seed + 2, lo, hi, n * k)         # n x k row-major (op_y = T)
+        gx, gy, gc, ga, gb = X, Yt, cv, alpha, beta
+        if dtype == "f16":  # the test quantises the golden's inputs through fp16 (sddmm_test.cpp:171-181)
+            q = lambda a: o.ref_sddmm_f16_to_f32(o.ref_sddmm_f32_to_f16(a.astype(np.float32))).astype(np.float64)
+            gx, gy, gc = q(X), q(Yt), q(cv)
+            ga, gb = float(q(np.array([alpha]))[0]), float(q(np.array([beta]))[0])
+        gold = o.ref_sddmm_f64(m, n, k, gx, gy, ro, ci, gc, ga, gb, False, True)
+        out[f"{name}/shape"] = np.array([m, k, n])
+        out[f"{name}/scalars"] = np.array([alpha, beta])
+        out[f"{name}/dtype"] = np.array([dtype])
+        out[f"{name}/row_offsets"], out[f"{name}/col_ind"], out[f"{name}/c_init"] = ro, ci, cv
+        out[f"{name}/X"], out[f"{name}/Yt"], out[f"{name}/gold"] = X, Yt, gold
+    np.savez_compressed(OUT / "sddmm.npz", **out)
+
+
 if __name__ == "__main__":
     for name in ("spmv", "spmm35", "spmm22"):
         if not o.ref_available(name):
@@ -163,5 +241,7 @@ if __name__ == "__main__":
     spmm35_f16_i8()
     spmm22()
     spmv()
+    convert()
+    sddmm()
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")

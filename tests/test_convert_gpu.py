@@ -1,5 +1,7 @@
-"""GPU: aclsparseXcoo2csr against counting + prefix sum (what the reference computes,
-sparse/coo2csr/arch35/coo2csr_kernel.cpp), bit-exact."""
+"""GPU: the CSR producers (aclsparseXcoo2csr, aclsparseXcsrsort, aclsparseCsr2cscEx2), bit for bit against the
+oracle's restatements of the reference's goldens (Coo2CsrGolden, csrsortGolden, Csr2CscGolden: oracle/oracle.cpp,
+pinned to the reference headers by tests/test_oracle_pins.py) and against the committed fixtures those goldens
+produced (tests/golden/convert.npz)."""
 from __future__ import annotations
 
 import numpy as np
@@ -9,17 +11,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def count_and_scan(rows_idx, m, base):
-    counts = np.bincount(rows_idx - base, minlength=m)[:m] if rows_idx.size else np.zeros(m, np.int64)
-    out = np.zeros(m + 1, np.int64)
-    out[1:] = np.cumsum(counts)
-    return (out + base).astype(np.int32)
-
-
 @pytest.mark.parametrize("base", [0, 1])
 @pytest.mark.parametrize("m,nnz,empty", [(1, 1, 0.0), (7, 30, 0.0), (1000, 5000, 0.5), (4096, 0, 0.0), (0, 0, 0.0),
                                           (300000, 2000000, 0.2), (5, 100000, 0.6)])
-def test_coo2csr(pkg, handle, device, m, nnz, empty, base):
+def test_coo2csr(pkg, handle, device, oracle, m, nnz, empty, base):
     rng = np.random.default_rng(m * 31 + nnz + base)
     if m and nnz:
         live = np.flatnonzero(rng.random(m) >= empty)
@@ -28,7 +23,7 @@ def test_coo2csr(pkg, handle, device, m, nnz, empty, base):
         rows_idx = np.sort(rng.choice(live, size=nnz)).astype(np.int32) + base
     else:
         rows_idx = np.zeros(0, np.int32)
-    want = count_and_scan(rows_idx.astype(np.int64), m, base)
+    want = oracle.coo2csr(rows_idx, m, base)
     d_in = torch.from_numpy(rows_idx).to(device)
     d_out = torch.full((m + 1,), -7, dtype=torch.int32, device=device)
     from ctypes import c_void_p
@@ -66,21 +61,10 @@ def test_coo2csr_feeds_spmv(pkg, handle, device, oracle):
                            helpers.TOL["f32"], "coo2csr -> spmv")
 
 
-def stable_row_sort(rp, ci, base):
-    """Per row: stable argsort of the column indices (what the reference documents for P)."""
-    out_ci, perm = ci.copy(), np.arange(ci.size, dtype=np.int32)
-    for r in range(rp.size - 1):
-        s, e = rp[r] - base, rp[r + 1] - base
-        order = np.argsort(ci[s:e], kind="stable")
-        out_ci[s:e] = ci[s:e][order]
-        perm[s:e] = (s + order).astype(np.int32)
-    return out_ci, perm
-
-
 @pytest.mark.parametrize("base", [0, 1])
 @pytest.mark.parametrize("m,n,mean_len,dups", [(1, 1, 1, False), (50, 40, 12, True), (3000, 5000, 30, False),
                                                 (200, 100000, 3000, False), (20000, 300, 4, True), (64, 64, 0, False)])
-def test_csrsort(pkg, handle, device, m, n, mean_len, dups, base):
+def test_csrsort(pkg, handle, device, oracle, m, n, mean_len, dups, base):
     from ctypes import byref, c_size_t, c_void_p
     L = pkg.lib()
     rng = np.random.default_rng(m + 7 * n + base)
@@ -93,7 +77,7 @@ def test_csrsort(pkg, handle, device, m, n, mean_len, dups, base):
     cols = [rng.integers(0, n, size=int(k)) if dups else rng.permutation(n)[:int(k)] for k in lengths]
     ci = (np.concatenate(cols) if nnz else np.zeros(0)).astype(np.int32) + base
     rp = rp + base
-    want_ci, want_p = stable_row_sort(rp, ci, base)
+    want_ci, want_p = oracle.csrsort(rp, ci, np.arange(nnz, dtype=np.int32), base)
 
     d_rp, d_ci = torch.from_numpy(rp).to(device), torch.from_numpy(ci).to(device)
     d_p = torch.arange(nnz, dtype=torch.int32, device=device)
@@ -174,7 +158,7 @@ def test_csrsort_lets_the_blocked_long_row_kernel_in(pkg, handle, device, oracle
 @pytest.mark.parametrize("vt", ["f32", "f16", "bf16", "i8"])
 @pytest.mark.parametrize("base,numeric", [(0, True), (1, True), (0, False)])
 def test_csr2csc(pkg, handle, device, oracle, vt, base, numeric):
-    """Against a stable sort of the entries by column (entries of a column keep their row order), bit for bit."""
+    """Entries of a column keep their row order (the golden drops them into their columns row by row): bit for bit."""
     from ctypes import byref, c_size_t, c_void_p
     from ops_sparse_b200 import synth
     L, S = pkg.lib(), pkg
@@ -190,13 +174,9 @@ def test_csr2csc(pkg, handle, device, oracle, vt, base, numeric):
         val, acl = A.values.astype(np.float32), S.ACL_FLOAT
     else:
         val, acl = oracle.to_storage(A.values.astype(np.float32), vt), (S.ACL_FLOAT16 if vt == "f16" else S.ACL_BF16)
-    perm = np.argsort(A.col_ind, kind="stable")
-    row_of = np.repeat(np.arange(m, dtype=np.int32), np.diff(A.row_ptr))
-    want_ri = row_of[perm] + base
-    want_val = val[perm]
-    want_cp = np.zeros(n + 1, np.int64)
-    want_cp[1:] = np.cumsum(np.bincount(A.col_ind, minlength=n))
-    want_cp = (want_cp + base).astype(np.int32)
+    raw = val.view({1: np.uint8, 2: np.uint16, 4: np.uint32}[val.dtype.itemsize])
+    want_cp, want_ri, want_raw = oracle.csr2csc(m, n, A.row_ptr + base, A.col_ind + base, raw, base)
+    want_val = want_raw.view(val.dtype)
 
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
     d_rp, d_ci, d_v = dev(A.row_ptr + base), dev(A.col_ind + base), dev(val.view(np.uint8).reshape(nnz, -1))
@@ -260,3 +240,60 @@ def test_csr2csc_empty_matrix_and_transposed_product(pkg, handle, device, oracle
     scale = 1.5 * np.bincount(A.col_ind, weights=prod, minlength=n)[:n] + np.abs(0.5 * y)
     helpers.assert_rowwise(dy.values.cpu().numpy().astype(np.float64), gold.astype(np.float64), scale,
                            helpers.TOL["f32"], "A^T x through csr2csc")
+
+
+def test_fixtures_of_the_reference_goldens(pkg, handle, device, golden_dir):
+    """tests/golden/convert.npz: outputs of the reference's own golden functions, reproduced on the device."""
+    from ctypes import byref, c_size_t, c_void_p
+    L, S = pkg.lib(), pkg
+    z = np.load(golden_dir / "convert.npz")
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    P = lambda t: c_void_p(t.data_ptr()) if t.numel() else None
+    for name in z["coo_names"]:
+        for base in (0, 1):
+            k = f"coo/{name}/{base}"
+            rows, m = z[f"{k}/rows"], int(z[f"{k}/m"][0])
+            d_in, d_out = dev(rows), torch.full((m + 1,), -7, dtype=torch.int32, device=device)
+            assert L.aclsparseXcoo2csr(handle.raw, P(d_in), rows.size, m, c_void_p(d_out.data_ptr()), base) == 0
+            torch.cuda.synchronize()
+            assert np.array_equal(d_out.cpu().numpy(), z[f"{k}/row_ptr"]), k
+    for name in z["sort_names"]:
+        for base in (0, 1):
+            k = f"sort/{name}/{base}"
+            rp, ci, n = z[f"{k}/row_ptr"], z[f"{k}/col_ind"], int(z[f"{k}/n"][0])
+            m, nnz = rp.size - 1, ci.size
+            d_rp, d_ci = dev(rp), dev(ci)
+            d_p = torch.arange(nnz, dtype=torch.int32, device=device)
+            descr = c_void_p()
+            assert L.aclsparseCreateMatDescr(byref(descr)) == 0
+            L.aclsparseSetMatIndexBase(descr, base)
+            size = c_size_t()
+            assert L.aclsparseXcsrsort_bufferSizeExt(handle.raw, m, n, nnz, P(d_rp), P(d_ci), byref(size)) == 0
+            buf = torch.empty(max(size.value, 1), dtype=torch.uint8, device=device)
+            assert L.aclsparseXcsrsort(handle.raw, m, n, nnz, descr, P(d_rp), P(d_ci), P(d_p), P(buf)) == 0
+            torch.cuda.synchronize()
+            assert np.array_equal(d_ci.cpu().numpy(), z[f"{k}/col_out"]), k
+            assert np.array_equal(d_p.cpu().numpy(), z[f"{k}/perm_out"]), k
+            L.aclsparseDestroyMatDescr(descr)
+    for name in z["csc_names"]:
+        for base in (0, 1):
+            k = f"csc/{name}/{base}"
+            m, n = (int(v) for v in z[f"{k}/shape"])
+            rp, ci, val = z[f"{k}/row_ptr"], z[f"{k}/col_ind"], z[f"{k}/val"]
+            nnz = ci.size
+            d_rp, d_ci, d_v = dev(rp), dev(ci), dev(val.view(np.int32))
+            o_v = torch.zeros(max(nnz, 1), dtype=torch.int32, device=device)
+            o_cp = torch.full((n + 1,), -3, dtype=torch.int32, device=device)
+            o_ri = torch.full((max(nnz, 1),), -3, dtype=torch.int32, device=device)
+            size = c_size_t()
+            assert L.aclsparseCsr2cscEx2_bufferSize(handle.raw, m, n, nnz, None, None, None, None, None, None, S.ACL_FLOAT,
+                                                    1, base, 0, byref(size)) == 0
+            buf = torch.empty(max(size.value, 1), dtype=torch.uint8, device=device)
+            assert L.aclsparseCsr2cscEx2(handle.raw, m, n, nnz, P(d_v), c_void_p(d_rp.data_ptr()), P(d_ci),
+                                         c_void_p(o_v.data_ptr()), c_void_p(o_cp.data_ptr()),
+                                         c_void_p(o_ri.data_ptr()), S.ACL_FLOAT, 1, base, 0,
+                                         c_void_p(buf.data_ptr())) == 0
+            torch.cuda.synchronize()
+            assert np.array_equal(o_cp.cpu().numpy(), z[f"{k}/col_ptr"]), k
+            assert np.array_equal(o_ri.cpu().numpy()[:nnz], z[f"{k}/row_ind"]), k
+            assert np.array_equal(o_v.cpu().numpy()[:nnz].view(np.uint32), z[f"{k}/val_out"]), k

@@ -200,3 +200,87 @@ def test_ref_spmv_random(oracle, triple, trans):
     mine = oracle.spmv_typed(rp, ci, val, x, y, a, b, comp, vt, ot, trans=trans, cols=N, bf16_trunc=True)
     ref = oracle.ref_spmv(rp, ci, val, x, y, a, b, comp, vt, ot, trans=trans, cols=N)
     assert np.array_equal(mine, ref)
+
+
+# ---- CSR producers and SDDMM: the restatements against the committed fixtures (everywhere) and against the
+# reference's golden headers compiled in place (where oracle/_ref holds them) --------------------------------
+
+def test_fixture_convert(oracle, golden_dir):
+    z = np.load(golden_dir / "convert.npz")
+    for name in z["sort_names"]:
+        for base in (0, 1):
+            k = f"sort/{name}/{base}"
+            co, po = oracle.csrsort(z[f"{k}/row_ptr"], z[f"{k}/col_ind"], np.arange(z[f"{k}/col_ind"].size, dtype=np.int32), base)
+            assert np.array_equal(co, z[f"{k}/col_out"]) and np.array_equal(po, z[f"{k}/perm_out"]), k
+    for name in z["coo_names"]:
+        for base in (0, 1):
+            k = f"coo/{name}/{base}"
+            assert np.array_equal(oracle.coo2csr(z[f"{k}/rows"], int(z[f"{k}/m"][0]), base), z[f"{k}/row_ptr"]), k
+    for name in z["csc_names"]:
+        for base in (0, 1):
+            k = f"csc/{name}/{base}"
+            m, n = (int(v) for v in z[f"{k}/shape"])
+            cp, ri, vo = oracle.csr2csc(m, n, z[f"{k}/row_ptr"], z[f"{k}/col_ind"], z[f"{k}/val"], base)
+            assert np.array_equal(cp, z[f"{k}/col_ptr"]) and np.array_equal(ri, z[f"{k}/row_ind"]), k
+            assert np.array_equal(vo, z[f"{k}/val_out"]), k
+
+
+def sddmm_case(oracle, z, name):
+    """Inputs and golden of one fixture case, the golden's inputs quantised as the reference test does."""
+    m, k, n = (int(v) for v in z[f"{name}/shape"])
+    alpha, beta = (float(v) for v in z[f"{name}/scalars"])
+    dtype = str(z[f"{name}/dtype"][0])
+    X, Yt, c0 = z[f"{name}/X"], z[f"{name}/Yt"], z[f"{name}/c_init"]
+    gx, gy, gc, ga, gb = X, Yt, c0, alpha, beta
+    if dtype == "f16":
+        q = lambda a: oracle.f16_to_f32(oracle.f32_to_f16(np.asarray(a, np.float64).astype(np.float32))).astype(np.float64)
+        gx, gy, gc = q(X), q(Yt), q(c0)
+        ga, gb = float(q([alpha])[0]), float(q([beta])[0])
+    gold = oracle.sddmm_f64(m, n, k, gx, gy, z[f"{name}/row_offsets"], z[f"{name}/col_ind"], gc, ga, gb, False, True)
+    return m, k, n, alpha, beta, dtype, X, Yt, c0, gold
+
+
+def test_fixture_sddmm(oracle, golden_dir):
+    z = np.load(golden_dir / "sddmm.npz")
+    for name in z["names"]:
+        gold = sddmm_case(oracle, z, name)[-1]
+        assert np.array_equal(gold.view(np.uint64), z[f"{name}/gold"].view(np.uint64)), name
+
+
+def test_convert_and_sddmm_against_reference_headers(oracle):
+    if not (oracle.ref_available("convert") and oracle.ref_available("sddmm")):
+        pytest.skip("oracle/_ref holds no golden headers of the reference on this machine")
+    rng = np.random.default_rng(99)
+    for trial in range(25):
+        m, n = int(rng.integers(1, 300)), int(rng.integers(1, 400))
+        base = int(rng.integers(0, 2))
+        lengths = rng.integers(0, min(n, 60) + 1, size=m)
+        rp = np.zeros(m + 1, np.int32)
+        rp[1:] = np.cumsum(lengths)
+        ci = rng.integers(0, n, size=int(rp[-1])).astype(np.int32)      # duplicates, unsorted
+        perm = rng.permutation(ci.size).astype(np.int32)
+        a, b = oracle.csrsort(rp + base, ci + base, perm, base), oracle.ref_csrsort(rp + base, ci + base, perm, base)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+        rows = np.sort(rng.integers(-2, m + 2, size=int(rng.integers(0, 500)))).astype(np.int32) + base  # some out of range
+        assert np.array_equal(oracle.coo2csr(rows, m, base), oracle.ref_coo2csr(rows, m, base))
+        for dt in (np.uint8, np.uint16, np.uint32):
+            vals = rng.integers(0, 200, size=ci.size).astype(dt)
+            x, y = oracle.csr2csc(m, n, rp + base, ci + base, vals, base), oracle.ref_csr2csc(m, n, rp + base, ci + base, vals, base)
+            assert all(np.array_equal(p, q) for p, q in zip(x, y))
+        mm, nn, kk = int(rng.integers(1, 40)), int(rng.integers(1, 40)), int(rng.integers(1, 70))
+        ro, cc, cv = oracle.ref_sddmm_sparsity(mm, nn, float(rng.choice([0.0, 0.3, 1.0])), -1.0, 1.0, trial)
+        for opx in (False, True):
+            for opy in (False, True):
+                X, Y = rng.standard_normal(mm * kk), rng.standard_normal(kk * nn)
+                g1 = oracle.sddmm_f64(mm, nn, kk, X, Y, ro, cc, cv, 1.25, -0.5, opx, opy)
+                g2 = oracle.ref_sddmm_f64(mm, nn, kk, X, Y, ro, cc, cv, 1.25, -0.5, opx, opy)
+                assert np.array_equal(g1.view(np.uint64), g2.view(np.uint64))
+    # the frame's mixed-tolerance verdict and the SDDMM test's fp16 converters
+    allh = np.arange(65536, dtype=np.uint16)
+    assert np.array_equal(oracle.f16_to_f32(allh).view(np.uint32), oracle.ref_sddmm_f16_to_f32(allh).view(np.uint32))
+    x = (rng.standard_normal(200000) * 10.0 ** rng.integers(-9, 6, 200000)).astype(np.float32)
+    assert np.array_equal(oracle.f32_to_f16(x), oracle.ref_sddmm_f32_to_f16(x))
+    for kind, noise in (("f32", 1e-6), ("f32", 1e-3), ("f16", 1e-3), ("f16", 1e-2), ("bf16", 1e-2), ("bf16", 1e-1)):
+        g = rng.standard_normal(4000).astype(np.float32)
+        out = (g + noise * rng.standard_normal(4000)).astype(np.float32)
+        assert oracle.verify_mixed_tolerance(out, g, kind)[0] == oracle.ref_verify_mixed_tolerance(out, g, kind), (kind, noise)

@@ -179,3 +179,30 @@ def test_empty_pattern_and_status_codes(pkg, handle, device):
     for d, kill in ((X, L.aclsparseDestroyDnMat), (Y, L.aclsparseDestroyDnMat), (C, L.aclsparseDestroySpMat),
                     (Ch, L.aclsparseDestroySpMat)):
         kill(d)
+
+
+def test_fixtures_of_the_reference_golden(pkg, handle, device, oracle, golden_dir):
+    """tests/golden/sddmm.npz: rows of the reference's own SDDMM case table (its pattern generator, its seeds, its
+    fp64 golden with inputs quantised through fp16 where the case is fp16), judged as its test judges the device:
+    golden cast to fp32 (clamped to +-65504 for fp16), then the frame's mixed tolerance (test/sddmm/sddmm/arch35/
+    sddmm_test.cpp:262-292)."""
+    z = np.load(golden_dir / "sddmm.npz")
+    for name in z["names"]:
+        m, k, n = (int(v) for v in z[f"{name}/shape"])
+        alpha, beta = (float(v) for v in z[f"{name}/scalars"])
+        dtype = str(z[f"{name}/dtype"][0])
+        ro, ci = z[f"{name}/row_offsets"], z[f"{name}/col_ind"]
+        if ci.size == 0:
+            continue  # the reference test skips the value check of its empty case too
+        np_t = np.float32 if dtype == "f32" else np.float16
+        X = z[f"{name}/X"].astype(np.float32).astype(np_t).reshape(m, k)       # what the test uploads: fp64 -> fp32 (-> fp16)
+        Yt = z[f"{name}/Yt"].astype(np.float32).astype(np_t).reshape(n, k)
+        c0 = z[f"{name}/c_init"].astype(np.float32).astype(np_t).astype(np.float32)
+        flat = lambda a: a.astype(np.float32).reshape(-1)
+        got = run_sddmm(pkg, handle, device, ro, ci, c0, (flat(X), m, k, k), (flat(Yt), n, k, k), alpha, beta, m, n,
+                        False, True, "row", "row", dtype)
+        gold = z[f"{name}/gold"].astype(np.float32)
+        if dtype == "f16":
+            gold = np.clip(gold, -65504.0, 65504.0)
+        ok, st = oracle.verify_mixed_tolerance(got, gold, dtype)
+        assert ok, (name, st)
