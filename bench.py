@@ -606,6 +606,167 @@ def gpu_arm(args, synth, oracle):
         raise SystemExit(f"parity check against the CPU oracle failed for {bad}")
 
 
+# ------------------------------------------------------------------------------- operators next to the hot path
+
+def aux_arm(args, synth, oracle):
+    """`--op coo2csr | csrsort | csr2csc | sddmm`: the CSR producers and SDDMM on benchmark-size inputs (one GPU).
+    One JSON line: time per call (CUDA events), algorithmic bytes per call, the HBM roofline fraction, the CPU
+    golden restatement timed on this host, and a bit-exact (converters) / reference-verdict (SDDMM) parity check."""
+    import torch
+    from ctypes import byref, c_size_t, c_uint16, c_void_p
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product path has no CPU implementation")
+    pkg = entry.load_package()
+    from ops_sparse_b200 import api
+    L, S = pkg.lib(), pkg
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    h = api.Handle()
+    P = lambda t: c_void_p(t.data_ptr())
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    K = max(3, min(args.steps, 50))
+    peak, peak_src = measured_peaks()
+
+    def timed(fn, restore=None):
+        for _ in range(3):
+            if restore:
+                restore()
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(K):
+            if restore:
+                restore()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        return np.array(times)
+
+    if args.op in ("coo2csr", "csrsort", "csr2csc"):
+        cfg = synth.config2()
+        A = cfg["A"]
+        m, n, nnz = A.rows, A.cols, A.nnz
+        d_rp, d_ci = to(A.row_ptr), to(A.col_ind)
+    if args.op == "coo2csr":
+        rows = np.repeat(np.arange(m, dtype=np.int32), A.lengths())
+        d_rows, d_out = to(rows), torch.empty(m + 1, dtype=torch.int32, device=dev)
+        fn = lambda: api.check(L.aclsparseXcoo2csr(h.raw, P(d_rows), nnz, m, P(d_out), 0), "aclsparseXcoo2csr")
+        t = timed(fn)
+        t0 = time.perf_counter()
+        gold = oracle.coo2csr(rows, m, 0)
+        cpu_s = time.perf_counter() - t0
+        ok = bool(np.array_equal(d_out.cpu().numpy(), gold))
+        alg = 4 * nnz + 4 * (m + 1)
+        workload = {"workload": "coo2csr of the c2 pattern", "rows": m, "nnz": nnz}
+        kernels = "Coo2CsrKernel (a binary search per row offset)"
+    elif args.op == "csrsort":
+        rng = np.random.default_rng(7)
+        key = np.repeat(np.arange(m, dtype=np.int64), A.lengths()) * (1 << 21) + rng.integers(0, 1 << 21, nnz)
+        shuffled = A.col_ind[np.argsort(key, kind="stable")].astype(np.int32)  # every row's columns in random order
+        d_src = to(shuffled)
+        d_col, d_p = torch.empty_like(d_src), torch.empty(nnz, dtype=torch.int32, device=dev)
+        iota = torch.arange(nnz, dtype=torch.int32, device=dev)
+        descr = c_void_p()
+        api.check(L.aclsparseCreateMatDescr(byref(descr)), "aclsparseCreateMatDescr")
+        size = c_size_t()
+        api.check(L.aclsparseXcsrsort_bufferSizeExt(h.raw, m, n, nnz, P(d_rp), P(d_src), byref(size)), "bufferSizeExt")
+        buf = torch.empty(size.value, dtype=torch.uint8, device=dev)
+
+        def restore():
+            d_col.copy_(d_src)
+            d_p.copy_(iota)
+        fn = lambda: api.check(L.aclsparseXcsrsort(h.raw, m, n, nnz, descr, P(d_rp), P(d_col), P(d_p), P(buf)), "csrsort")
+        t = timed(fn, restore)
+        t0 = time.perf_counter()
+        gc_, gp_ = oracle.csrsort(A.row_ptr, shuffled, np.arange(nnz, dtype=np.int32), 0)
+        cpu_s = time.perf_counter() - t0
+        ok = bool(np.array_equal(d_col.cpu().numpy(), gc_) and np.array_equal(d_p.cpu().numpy(), gp_))
+        alg = 4 * (m + 1) + 16 * nnz  # col_ind and P: read once, written once
+        workload = {"workload": "csrsort of the c2 pattern, columns shuffled inside every row", "rows": m, "nnz": nnz,
+                    "workspace_bytes": int(size.value)}
+        kernels = "CsrsortPackKernel + SegSortShortKernel + SegSortLongKernel + CsrsortUnpackKernel + D2D copy of P"
+    elif args.op == "csr2csc":
+        d_v = to(A.values)
+        o_v, o_ri = torch.empty_like(d_v), torch.empty_like(d_ci)
+        o_cp = torch.empty(n + 1, dtype=torch.int32, device=dev)
+        size = c_size_t()
+        api.check(L.aclsparseCsr2cscEx2_bufferSize(h.raw, m, n, nnz, None, None, None, None, None, None, S.ACL_FLOAT, 1, 0,
+                                                   0, byref(size)), "bufferSize")
+        buf = torch.empty(size.value, dtype=torch.uint8, device=dev)
+        fn = lambda: api.check(L.aclsparseCsr2cscEx2(h.raw, m, n, nnz, P(d_v), P(d_rp), P(d_ci), P(o_v), P(o_cp), P(o_ri),
+                                                     S.ACL_FLOAT, 1, 0, 0, P(buf)), "csr2csc")
+        t = timed(fn)
+        t0 = time.perf_counter()
+        gcp, gri, gv = oracle.csr2csc(m, n, A.row_ptr, A.col_ind, A.values.view(np.uint32), 0)
+        cpu_s = time.perf_counter() - t0
+        ok = bool(np.array_equal(o_cp.cpu().numpy(), gcp) and np.array_equal(o_ri.cpu().numpy(), gri)
+                  and np.array_equal(o_v.cpu().numpy().view(np.uint32), gv))
+        alg = 4 * (m + 1) + 8 * nnz + 4 * (n + 1) + 8 * nnz
+        workload = {"workload": "csr2csc (numeric, fp32) of the c2 matrix", "rows": m, "cols": n, "nnz": nnz,
+                    "workspace_bytes": int(size.value)}
+        kernels = ("ColumnHistogramKernel + Scan{BlockSums,Sums,Apply}Kernel + ScatterKeysKernel + SegSort{Short,Long}Kernel"
+                   " + GatherKernel")
+    else:  # sddmm: the pattern of a 1 M-node power-law graph, X and Y^T of 256 fp16 per row (the backward of c5's layer)
+        cfg = synth.config5(rows=1 << 20)
+        A = cfg["A"]
+        m, n, nnz, k = A.rows, A.cols, A.nnz, 256
+        rng = np.random.default_rng(11)
+        X = torch.from_numpy(rng.uniform(-1, 1, (m, k)).astype(np.float16)).to(dev)
+        Yt = torch.from_numpy(rng.uniform(-1, 1, (n, k)).astype(np.float16)).to(dev)
+        c0 = torch.from_numpy(rng.uniform(-1, 1, nnz).astype(np.float16)).to(dev)
+        cv = c0.clone()
+        d_rp, d_ci = to(A.row_ptr), to(A.col_ind)
+        dX, dY, dC = c_void_p(), c_void_p(), c_void_p()
+        api.check(L.aclsparseCreateDnMat(byref(dX), m, k, k, P(X), S.ACL_FLOAT16, 0), "CreateDnMat")
+        api.check(L.aclsparseCreateDnMat(byref(dY), n, k, k, P(Yt), S.ACL_FLOAT16, 0), "CreateDnMat")
+        api.check(L.aclsparseCreateCsr(byref(dC), m, n, nnz, P(d_rp), P(d_ci), P(cv), 0, 0, 0, S.ACL_FLOAT16), "CreateCsr")
+        one, half = c_uint16(int(np.float16(1.0).view(np.uint16))), c_uint16(int(np.float16(0.5).view(np.uint16)))
+        a_, b_ = c_void_p(ctypes.addressof(one)), c_void_p(ctypes.addressof(half))
+        size = c_size_t()
+        api.check(L.aclsparseSDDMMBufferSize(h.raw, 0, 1, a_, dX, dY, b_, dC, S.ACL_FLOAT16, 0, byref(size)), "BufferSize")
+        buf = torch.empty(max(size.value, 256), dtype=torch.uint8, device=dev)
+        api.check(L.aclsparseSDDMMPreprocess(h.raw, 0, 1, a_, dX, dY, b_, dC, S.ACL_FLOAT16, 0, P(buf)), "Preprocess")
+        fn = lambda: api.check(L.aclsparseSDDMM(h.raw, 0, 1, a_, dX, dY, b_, dC, S.ACL_FLOAT16, 0, P(buf)), "aclsparseSDDMM")
+        t = timed(fn, lambda: cv.copy_(c0))
+        # parity and CPU time on the leading rows (the fp64 golden is O(nnz * k) on one thread)
+        rows_s = int(np.searchsorted(A.row_ptr, 200_000))
+        e_s = int(A.row_ptr[rows_s])
+        Xs = X[:rows_s].to(torch.float64).cpu().numpy()
+        Ys = Yt.to(torch.float64).cpu().numpy()
+        t0 = time.perf_counter()
+        gold = oracle.sddmm_f64(rows_s, n, k, Xs, Ys, A.row_ptr[:rows_s + 1], A.col_ind[:e_s],
+                                c0[:e_s].to(torch.float64).cpu().numpy(), 1.0, 0.5, False, True)
+        cpu_s = (time.perf_counter() - t0) * (nnz / max(e_s, 1))
+        got = cv[:e_s].to(torch.float32).cpu().numpy()
+        ok = oracle.verify_mixed_tolerance(got, np.clip(gold.astype(np.float32), -65504.0, 65504.0), "f16")[0]
+        alg = 2 * m * k + 2 * n * k + 4 * (m + 1) + 4 * nnz + 4 * nnz
+        workload = {"workload": "SDDMM fp16 on the pattern of a 1,048,576-node power-law graph, k = 256, op_y = T",
+                    "rows": m, "cols": n, "nnz": nnz, "k": k, "alpha": 1.0, "beta": 0.5,
+                    "gather_bytes": int(nnz) * 2 * k * 2,
+                    "note": "the Y row of every entry is its own 512-byte read: the gather (nnz * 1 KB with X) is what "
+                            "moves, the algorithmic bytes count X and Y once"}
+        kernels = "SddmmKernel"
+    ms = float(np.median(t))
+    line = {"op": args.op, "metric": f"{args.op}_ms", "value": ms, "unit": "ms", "higher_is_better": False, "n_gpus": 1,
+            "steps": K, "warmup": 3, "per_step_ms": {"min": float(t.min()), "median": ms, "max": float(t.max())},
+            "data": "synthetic (seeded)", "config": workload,
+            "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": int(alg),
+                         "peak_source": peak_src, "kernel": kernels, "traffic": None},
+            "cpu_baseline": {"value": cpu_s * 1e3, "unit": "ms", "cores": 1, "kind": "port",
+                             "sample": "oracle restatement of the reference golden, one pass on one thread"
+                                       + (" (leading rows, scaled by nnz)" if args.op == "sddmm" else "")},
+            "parity": {"ok": bool(ok), "rule": "bit-exact against the golden restatement" if args.op != "sddmm" else
+                       "mixed tolerance of the reference test frame on the leading 200,000 entries' rows"}}
+    print(json.dumps(line))
+    h.close()
+    if not ok:
+        raise SystemExit(f"{args.op}: parity check against the CPU oracle failed")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -618,6 +779,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU golden timing leg")
     ap.add_argument("--replicate", default="peer", choices=["peer", "nccl-allgather", "nccl-broadcast"],
                     help="how x / B reaches every GPU inside a multi-GPU step (see ops-sparse_b200/mg.py)")
+    ap.add_argument("--op", default="", choices=["", "coo2csr", "csrsort", "csr2csc", "sddmm"],
+                    help="measure one of the operators next to the hot path instead (one GPU)")
     ap.add_argument("--no-graph", action="store_true", help="end-to-end leg: issue every step's operations one by one")
     ap.add_argument("--e2e-panels", type=int, default=4,
                     help="row panels the end-to-end leg pipelines its host copies over (1 = copy, compute, copy)")
@@ -632,7 +795,10 @@ def main():
     else:
         entry.load_package()
         from ops_sparse_b200 import synth
-        gpu_arm(args, synth, oracle)
+        if args.op:
+            aux_arm(args, synth, oracle)
+        else:
+            gpu_arm(args, synth, oracle)
 
 
 if __name__ == "__main__":

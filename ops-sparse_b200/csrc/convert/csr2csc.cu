@@ -1,22 +1,26 @@
 // aclsparseCsr2cscEx2: CSR -> CSC (the transpose's CSR), structure and optionally values.
 // Checks, their order and status codes follow the reference host layer
 // (sparse/csr2csc_ex2/arch35/csr2csc_ex2_host.cpp:44-57, 106-232, 255-288, 539-640).
-// Entries of one column keep their row order (the reference scatters stripes in ascending entry order for
-// the same reason), so the result is unique and the tests compare it bit for bit.
+// Entries of one column keep their row order (the golden drops them into their columns row by row,
+// test/csr2csc_ex2/csr2csc_ex2_golden.h:50-110), so the result is unique and the tests compare it bit for bit.
 //
-// Here: a stable key-value radix sort of (column, entry index) -- CUB's device radix sort, a library
-// routine: this converter is off the SpMV / SpMM hot path -- then three small kernels: column offsets by
-// binary search in the sorted columns, the row of every entry by binary search in the CSR row offsets,
-// and the gather of the values through the permutation.  A CSC copy of A gives y = A^T x without
-// atomics: aclsparseSpMV (non-transposed) on the CSC arrays read as CSR.
+// Here, with kernels of this library only:
+//   1. a histogram of the columns (one atomic add per entry) into cscColPtr;
+//   2. an exclusive scan of it (block sums, a one-CTA scan of the sums, a second sweep) -> the column offsets;
+//   3. every entry is dropped into SOME free slot of its column (an atomic cursor per column) as a 64-bit key:
+//      entry index in the high word, row in the low word;
+//   4. every column segment is sorted by that key (segsort.cuh): ascending entry index IS the golden's order,
+//      whatever order the atomics produced;
+//   5. the keys are split again: row index from the low word, value fetched through the high word.
+// A CSC copy of A gives y = A^T x without atomics: aclsparseSpMV (non-transposed) on the CSC arrays read as CSR.
 #include <climits>
 #include <cstdint>
 
-#include <cub/device/device_radix_sort.cuh>
 #include <cuda_runtime.h>
 
 #include "b200sp_kernels.h"
 #include "common/internal.h"
+#include "convert/segsort.cuh"
 
 namespace {
 
@@ -51,64 +55,140 @@ aclsparseStatus_t ValidateCommon(aclsparseHandle_t handle, int m, int n, int nnz
 }
 
 struct Layout {
-    size_t offIota, offKeys, offPerm, offTemp, total;
+    size_t offKeys, offScratch, offCursor, offSums, offList, total;
 };
-Layout LayoutFor(int nnz, size_t tempBytes)
+constexpr int kScanBlock = 1024;  // counts one CTA scans in one sweep
+Layout LayoutFor(int n, int nnz)
 {
-    const size_t arr = AlignUp(sizeof(int32_t) * (size_t)nnz, 256);
+    const size_t keys = AlignUp(sizeof(unsigned long long) * (size_t)nnz, 256);
     Layout L;
-    L.offIota = 0;
-    L.offKeys = arr;
-    L.offPerm = 2 * arr;
-    L.offTemp = 3 * arr;
-    L.total = 3 * arr + AlignUp(tempBytes, 256);
+    L.offKeys = 0;
+    L.offScratch = keys;
+    L.offCursor = 2 * keys;
+    L.offSums = L.offCursor + AlignUp(sizeof(int32_t) * ((size_t)n + 1), 256);
+    L.offList = L.offSums + AlignUp(sizeof(int32_t) * ((size_t)n / kScanBlock + 2), 256);
+    L.total = L.offList + b200sp_segsort::ListBytes(n);
     return L;
 }
 
-cudaError_t SortCall(void *temp, size_t &tempBytes, const int *keysIn, int *keysOut, const int *valsIn, int *valsOut,
-                     int nnz, int n, cudaStream_t st)
+__global__ void FillKernel(int *out, long long count, int value)
 {
-    int bits = 1;  // column indices (with the base) are below n + 1
-    while (bits < 31 && (1ll << bits) <= (long long)n + 1) ++bits;
-    return cub::DeviceRadixSort::SortPairs(temp, tempBytes, keysIn, keysOut, valsIn, valsOut, nnz, 0, bits, st);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        out[i] = value;
 }
 
-__global__ void IotaKernel(int *out, int n)
+// counts[col] += 1 for every entry (counts has n + 1 slots, zeroed before; slot n stays 0)
+__global__ void ColumnHistogramKernel(const int *__restrict__ colInd, int nnz, int base, int *__restrict__ counts)
 {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        out[i] = (int)i;
+    for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < nnz; k += (long long)gridDim.x * blockDim.x)
+        atomicAdd(counts + (__ldg(colInd + k) - base), 1);
 }
 
-// out[i] = base + |{k : sorted[k] < i + base}| for i = 0..n: the offsets of the runs of equal keys.
-__global__ void RunOffsetsKernel(const int *__restrict__ sorted, int nnz, int n, int *__restrict__ out, int base)
+// Exclusive scan of count values in place, in three steps.  Step 1: the sum of every kScanBlock-wide block.
+__global__ void __launch_bounds__(256) ScanBlockSumsKernel(const int *__restrict__ v, long long count, int *__restrict__ sums)
 {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i <= n; i += (long long)gridDim.x * blockDim.x) {
-        const int key = (int)i + base;
-        int lo = 0, hi = nnz;
-        while (lo < hi) {
-            const int mid = lo + ((hi - lo) >> 1);
-            if (__ldg(sorted + mid) < key) lo = mid + 1;
-            else hi = mid;
-        }
-        out[i] = lo + base;
+    __shared__ int sWarp[8];
+    const long long b0 = (long long)blockIdx.x * kScanBlock;
+    int acc = 0;
+    for (int i = threadIdx.x; i < kScanBlock; i += 256)
+        if (b0 + i < count) acc += v[b0 + i];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if ((threadIdx.x & 31) == 0) sWarp[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < 8; ++w) t += sWarp[w];
+        sums[blockIdx.x] = t;
     }
 }
 
-// cscRowInd[k] = row that holds entry perm[k]; cscVal[k] = csrVal[perm[k]] (kBytes per value, 0 = no values).
+// Inclusive scan of the calling CTA's 256 values (one per thread); returns this thread's inclusive prefix.
+__device__ __forceinline__ int CtaInclusiveScan(int x, int *sWarp)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += t;
+    }
+    if (lane == 31) sWarp[warp] = x;
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += sWarp[w];
+    __syncthreads();
+    return x + before;
+}
+
+// Step 2: exclusive scan of the block sums by one CTA, 256 at a time with a running carry.
+__global__ void __launch_bounds__(256) ScanSumsKernel(int *__restrict__ sums, int blocks)
+{
+    __shared__ int sWarp[8];
+    __shared__ int sCarry;
+    if (threadIdx.x == 0) sCarry = 0;
+    __syncthreads();
+    for (int b0 = 0; b0 < blocks; b0 += 256) {
+        const int i = b0 + threadIdx.x;
+        const int x = i < blocks ? sums[i] : 0;
+        const int incl = CtaInclusiveScan(x, sWarp);
+        const int carry = sCarry;
+        if (i < blocks) sums[i] = carry + incl - x;
+        __syncthreads();
+        if (threadIdx.x == 255) sCarry = carry + incl;
+        __syncthreads();
+    }
+}
+
+// Step 3: exclusive scan inside every block plus the block's offset; `plus` (the index base) is added to every
+// result written to out, the zero-based result also goes to cursor (the next free slot of every column).
+__global__ void __launch_bounds__(256) ScanApplyKernel(const int *__restrict__ v, long long count,
+                                                       const int *__restrict__ sums, int plus, int *__restrict__ out,
+                                                       int *__restrict__ cursor)
+{
+    __shared__ int sWarp[8];
+    const long long b0 = (long long)blockIdx.x * kScanBlock;
+    int carry = sums[blockIdx.x];
+    for (int c = 0; c < kScanBlock; c += 256) {
+        const long long i = b0 + c + threadIdx.x;
+        const int x = i < count ? v[i] : 0;
+        const int incl = CtaInclusiveScan(x, sWarp);
+        if (i < count) {
+            out[i] = carry + incl - x + plus;
+            cursor[i] = carry + incl - x;
+        }
+        __shared__ int sTotal;
+        if (threadIdx.x == 255) sTotal = incl;
+        __syncthreads();
+        carry += sTotal;
+        __syncthreads();
+    }
+}
+
+// A warp per row: every entry takes the next free slot of its column and leaves (entry index, row) there.
+__global__ void __launch_bounds__(256) ScatterKeysKernel(const int *__restrict__ rowPtr, const int *__restrict__ colInd,
+                                                         int m, int base, int *__restrict__ cursor,
+                                                         unsigned long long *__restrict__ keys)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < m; r += warpsTotal) {
+        const int a = rowPtr[r] - base, b = rowPtr[r + 1] - base;
+        for (int e = a + lane; e < b; e += 32) {
+            const int slot = atomicAdd(cursor + (colInd[e] - base), 1);
+            keys[slot] = ((unsigned long long)(unsigned)e << 32) | (unsigned)r;
+        }
+    }
+}
+
+// cscRowInd[k] = low word + base; cscVal[k] = csrVal[high word] (kBytes per value, 0 = no values).
 template <int kBytes>
-__global__ void GatherKernel(const int *__restrict__ perm, const int *__restrict__ csrRowPtr, int m, int base,
-                             const void *__restrict__ csrVal, int nnz, int *__restrict__ cscRowInd,
-                             void *__restrict__ cscVal)
+__global__ void GatherKernel(const unsigned long long *__restrict__ keys, int base, const void *__restrict__ csrVal,
+                             int nnz, int *__restrict__ cscRowInd, void *__restrict__ cscVal)
 {
     for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < nnz; k += (long long)gridDim.x * blockDim.x) {
-        const int p = perm[k];
-        int lo = 0, hi = m - 1;  // largest r with csrRowPtr[r] - base <= p
-        while (lo < hi) {
-            const int mid = lo + ((hi - lo + 1) >> 1);
-            if (__ldg(csrRowPtr + mid) - base <= p) lo = mid;
-            else hi = mid - 1;
-        }
-        cscRowInd[k] = lo + base;
+        const unsigned long long key = keys[k];
+        const unsigned p = (unsigned)(key >> 32);
+        cscRowInd[k] = (int)(unsigned)(key & 0xffffffffu) + base;
         if constexpr (kBytes == 1) static_cast<uint8_t *>(cscVal)[k] = static_cast<const uint8_t *>(csrVal)[p];
         if constexpr (kBytes == 2) static_cast<uint16_t *>(cscVal)[k] = static_cast<const uint16_t *>(csrVal)[p];
         if constexpr (kBytes == 4) static_cast<uint32_t *>(cscVal)[k] = static_cast<const uint32_t *>(csrVal)[p];
@@ -140,14 +220,7 @@ aclsparseStatus_t aclsparseCsr2cscEx2_bufferSize(aclsparseHandle_t handle, int m
         *bufferSize = 0;
         return ACL_SPARSE_STATUS_SUCCESS;
     }
-    size_t tempBytes = 0;  // a size query: nothing is launched
-    const cudaError_t e = SortCall(nullptr, tempBytes, nullptr, nullptr, nullptr, nullptr, nnz, n, nullptr);
-    if (e != cudaSuccess) {
-        B200SP_LOGE("aclsparseCsr2cscEx2_bufferSize: size query failed (%s)", cudaGetErrorString(e));
-        (void)cudaGetLastError();
-        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
-    }
-    *bufferSize = LayoutFor(nnz, tempBytes).total;
+    *bufferSize = LayoutFor(n, nnz).total;  // from the sizes alone: nothing is launched
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
@@ -173,37 +246,48 @@ aclsparseStatus_t aclsparseCsr2cscEx2(aclsparseHandle_t handle, int m, int n, in
 
     cudaStream_t stream = handle->stream;
     if (nnz == 0) {  // every column is empty: n + 1 offsets equal to the base
-        RunOffsetsKernel<<<Blocks((long long)n + 1), 256, 0, stream>>>(nullptr, 0, n, cscColPtr, base);
+        FillKernel<<<Blocks((long long)n + 1), 256, 0, stream>>>(cscColPtr, (long long)n + 1, base);
         b200sp_note_launches(1);
         return cudaGetLastError() == cudaSuccess ? ACL_SPARSE_STATUS_SUCCESS : ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
     if (buffer == nullptr) return ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES;  // csr2csc_ex2_host.cpp:298-310
 
-    size_t tempBytes = 0;
-    cudaError_t e = SortCall(nullptr, tempBytes, nullptr, nullptr, nullptr, nullptr, nnz, n, stream);
-    if (e != cudaSuccess) return ACL_SPARSE_STATUS_EXECUTION_FAILED;
-    const Layout L = LayoutFor(nnz, tempBytes);
+    const Layout L = LayoutFor(n, nnz);
     char *p = static_cast<char *>(buffer);
-    int *iota = reinterpret_cast<int *>(p + L.offIota);
-    int *keys = reinterpret_cast<int *>(p + L.offKeys);
-    int *perm = reinterpret_cast<int *>(p + L.offPerm);
-    IotaKernel<<<Blocks(nnz), 256, 0, stream>>>(iota, nnz);
-    e = SortCall(p + L.offTemp, tempBytes, csrColInd, keys, iota, perm, nnz, n, stream);
+    auto *keys = reinterpret_cast<unsigned long long *>(p + L.offKeys);
+    auto *scratch = reinterpret_cast<unsigned long long *>(p + L.offScratch);
+    int *cursor = reinterpret_cast<int *>(p + L.offCursor);
+    int *sums = reinterpret_cast<int *>(p + L.offSums);
+    int *list = reinterpret_cast<int *>(p + L.offList);
+    const long long counts = (long long)n + 1;
+    const int scanBlocks = (int)((counts + kScanBlock - 1) / kScanBlock);
+    const long long warpRows = ((long long)m + 7) / 8;
+    const long long cap = (long long)b200sp_sm_count() * 32;
+    cudaError_t e = cudaMemsetAsync(cscColPtr, 0, sizeof(int) * (size_t)counts, stream);
+    if (e != cudaSuccess) return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+    ColumnHistogramKernel<<<Blocks(nnz), 256, 0, stream>>>(csrColInd, nnz, base, cscColPtr);
+    ScanBlockSumsKernel<<<(unsigned)scanBlocks, 256, 0, stream>>>(cscColPtr, counts, sums);
+    ScanSumsKernel<<<1, 256, 0, stream>>>(sums, scanBlocks);
+    ScanApplyKernel<<<(unsigned)scanBlocks, 256, 0, stream>>>(cscColPtr, counts, sums, base, cscColPtr, cursor);
+    ScatterKeysKernel<<<(unsigned)(warpRows < 1 ? 1 : (warpRows < cap ? warpRows : cap)), 256, 0, stream>>>(
+        csrRowPtr, csrColInd, m, base, cursor, keys);
+    b200sp_note_launches(5);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = b200sp_segsort::Sort(cscColPtr, base, n, keys, scratch, list, stream);
     if (e != cudaSuccess) {
         B200SP_LOGE("aclsparseCsr2cscEx2: sort failed (%s)", cudaGetErrorString(e));
         (void)cudaGetLastError();
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
-    RunOffsetsKernel<<<Blocks((long long)n + 1), 256, 0, stream>>>(keys, nnz, n, cscColPtr, base);
     const int bytes = numeric ? ValueBytes(valType) : 0;
     const unsigned g = Blocks(nnz);
     switch (bytes) {
-        case 1: GatherKernel<1><<<g, 256, 0, stream>>>(perm, csrRowPtr, m, base, csrVal, nnz, cscRowInd, cscVal); break;
-        case 2: GatherKernel<2><<<g, 256, 0, stream>>>(perm, csrRowPtr, m, base, csrVal, nnz, cscRowInd, cscVal); break;
-        case 4: GatherKernel<4><<<g, 256, 0, stream>>>(perm, csrRowPtr, m, base, csrVal, nnz, cscRowInd, cscVal); break;
-        default: GatherKernel<0><<<g, 256, 0, stream>>>(perm, csrRowPtr, m, base, nullptr, nnz, cscRowInd, nullptr); break;
+        case 1: GatherKernel<1><<<g, 256, 0, stream>>>(keys, base, csrVal, nnz, cscRowInd, cscVal); break;
+        case 2: GatherKernel<2><<<g, 256, 0, stream>>>(keys, base, csrVal, nnz, cscRowInd, cscVal); break;
+        case 4: GatherKernel<4><<<g, 256, 0, stream>>>(keys, base, csrVal, nnz, cscRowInd, cscVal); break;
+        default: GatherKernel<0><<<g, 256, 0, stream>>>(keys, base, nullptr, nnz, cscRowInd, nullptr); break;
     }
-    b200sp_note_launches(3);
+    b200sp_note_launches(1);
     e = cudaGetLastError();
     if (e != cudaSuccess) {
         B200SP_LOGE("aclsparseCsr2cscEx2: kernel launch failed (%s)", cudaGetErrorString(e));

@@ -2,22 +2,22 @@
 // carried along; and the legacy matrix descriptor it takes its index base from.
 // Checks, their order and status codes follow the reference host layer
 // (sparse/csrsort/arch35/csrsort_host.cpp:52-74, 146-222; sparse/common/aclsparse_matdescr.cpp:25-108).
-// The sort itself is CUB's segmented stable sort (a library routine: this converter is not on the SpMV /
-// SpMM hot path, it prepares its input -- ascending columns are what lets the long-row SpMV kernel cut
-// rows at the block boundaries of x).  Sorted keys and values land in the caller's workspace and are
-// copied back; the workspace therefore holds 8 bytes per entry (what the reference asks for) plus CUB's
-// own temporary storage.
+// The sort: every entry becomes a 64-bit key (column in the high word, position inside its row in the low word),
+// which makes keys unique and the ascending order of keys exactly the stable order the golden defines
+// (test/csrsort/arch35/csrsort_golden.h:38-70); the rows are then sorted by the segmented sort of segsort.cuh
+// (registers for rows of up to 32 entries, shared memory up to 2048, chunk sort + merge passes beyond), and a last
+// pass splits the keys again: the high word is the sorted column, the low word says which entry of P moves here.
+// Workspace: 8 bytes per entry for the keys, 8 for the merge scratch (whose first half also holds the permuted P
+// until it is copied back) and a list of the rows too long for a warp.
 #include <cstdint>
 #include <limits>
 #include <new>
 
-#include <cub/device/device_segmented_sort.cuh>
-#include <cub/iterator/counting_input_iterator.cuh>
-#include <cub/iterator/transform_input_iterator.cuh>
 #include <cuda_runtime.h>
 
 #include "b200sp_kernels.h"
 #include "common/internal.h"
+#include "convert/segsort.cuh"
 
 struct aclsparseMatDescr {  // aclsparse_descr_internal.h:131-136
     aclsparseMatrixType_t type = ACL_SPARSE_MATRIX_TYPE_GENERAL;
@@ -27,13 +27,6 @@ struct aclsparseMatDescr {  // aclsparse_descr_internal.h:131-136
 };
 
 namespace {
-
-struct MinusBase {  // row offsets with the index base taken off
-    const int *p;
-    int base;
-    __host__ __device__ int operator()(int i) const { return p[i] - base; }
-};
-using OffsetIt = cub::TransformInputIterator<int, MinusBase, cub::CountingInputIterator<int>>;
 
 inline size_t AlignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -46,13 +39,56 @@ aclsparseStatus_t ValidateCommon(int m, int n, int nnz, const int *csrRowPtr, co
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
-cudaError_t SortCall(void *temp, size_t &tempBytes, const int *keysIn, int *keysOut, const int *valsIn, int *valsOut,
-                     int nnz, int m, const int *rowPtr, int base, cudaStream_t st)
+struct SortLayout {
+    size_t offKeys, offScratch, offList, total;
+};
+SortLayout SortLayoutFor(int m, int nnz)
 {
-    OffsetIt begin(cub::CountingInputIterator<int>(0), MinusBase{rowPtr, base});
-    OffsetIt end(cub::CountingInputIterator<int>(1), MinusBase{rowPtr, base});
-    return cub::DeviceSegmentedSort::StableSortPairs(temp, tempBytes, keysIn, keysOut, valsIn, valsOut, nnz, m, begin,
-                                                     end, st);
+    SortLayout L;
+    const size_t keys = AlignUp(sizeof(unsigned long long) * (size_t)nnz, 256);
+    L.offKeys = 0;
+    L.offScratch = keys;
+    L.offList = 2 * keys;
+    L.total = 2 * keys + b200sp_segsort::ListBytes(m);
+    return L;
+}
+
+// A warp per row: keys[e] = column << 32 | (e - row start).
+__global__ void __launch_bounds__(256) CsrsortPackKernel(const int *__restrict__ rowPtr, const int *__restrict__ colInd,
+                                                         int m, int base, unsigned long long *__restrict__ keys)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < m; r += warpsTotal) {
+        const int a = rowPtr[r] - base, b = rowPtr[r + 1] - base;
+        for (int e = a + lane; e < b; e += 32)
+            keys[e] = ((unsigned long long)(unsigned)colInd[e] << 32) | (unsigned)(e - a);
+    }
+}
+
+// A warp per row: colInd[e] = high word of keys[e]; permuted[e] = P[row start + low word].
+__global__ void __launch_bounds__(256) CsrsortUnpackKernel(const int *__restrict__ rowPtr, int m, int base,
+                                                           const unsigned long long *__restrict__ keys,
+                                                           int *__restrict__ colInd, const int *__restrict__ P,
+                                                           int *__restrict__ permuted)
+{
+    const int lane = threadIdx.x & 31;
+    const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < m; r += warpsTotal) {
+        const int a = rowPtr[r] - base, b = rowPtr[r + 1] - base;
+        for (int e = a + lane; e < b; e += 32) {
+            const unsigned long long k = keys[e];
+            colInd[e] = (int)(unsigned)(k >> 32);
+            permuted[e] = P[a + (int)(unsigned)(k & 0xffffffffu)];
+        }
+    }
+}
+
+unsigned WarpRowBlocks(int m)
+{
+    const long long want = ((long long)m + 7) / 8;
+    const long long cap = (long long)b200sp_sm_count() * 32;
+    return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
 }  // namespace
@@ -94,14 +130,7 @@ aclsparseStatus_t aclsparseXcsrsort_bufferSizeExt(aclsparseHandle_t handle, int 
         *pBufferSizeInBytes = 0;
         return ACL_SPARSE_STATUS_SUCCESS;
     }
-    size_t tempBytes = 0;  // a size query: nothing is launched, nothing is read
-    const cudaError_t e = SortCall(nullptr, tempBytes, nullptr, nullptr, nullptr, nullptr, nnz, m, csrRowPtr, 0, nullptr);
-    if (e != cudaSuccess) {
-        B200SP_LOGE("aclsparseXcsrsort_bufferSizeExt: size query failed (%s)", cudaGetErrorString(e));
-        (void)cudaGetLastError();
-        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
-    }
-    *pBufferSizeInBytes = 2 * AlignUp(sizeof(int32_t) * (size_t)nnz, 256) + AlignUp(tempBytes, 256);
+    *pBufferSizeInBytes = SortLayoutFor(m, nnz).total;  // computed from the sizes alone: nothing is read
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
@@ -119,17 +148,25 @@ aclsparseStatus_t aclsparseXcsrsort(aclsparseHandle_t handle, int m, int n, int 
     if (pBuffer == nullptr) return ACL_SPARSE_STATUS_INVALID_VALUE;
 
     cudaStream_t stream = handle->stream;
-    const size_t half = AlignUp(sizeof(int32_t) * (size_t)nnz, 256);
-    auto *keysOut = static_cast<int *>(pBuffer);
-    auto *valsOut = reinterpret_cast<int *>(static_cast<char *>(pBuffer) + half);
-    void *temp = static_cast<char *>(pBuffer) + 2 * half;
-    size_t tempBytes = 0;
+    const SortLayout L = SortLayoutFor(m, nnz);
+    char *w = static_cast<char *>(pBuffer);
+    auto *keys = reinterpret_cast<unsigned long long *>(w + L.offKeys);
+    auto *scratch = reinterpret_cast<unsigned long long *>(w + L.offScratch);
+    auto *list = reinterpret_cast<int *>(w + L.offList);
     const int b = base == ACL_SPARSE_INDEX_BASE_ONE ? 1 : 0;
-    cudaError_t e = SortCall(nullptr, tempBytes, csrColInd, keysOut, P, valsOut, nnz, m, csrRowPtr, b, stream);
-    if (e == cudaSuccess) e = SortCall(temp, tempBytes, csrColInd, keysOut, P, valsOut, nnz, m, csrRowPtr, b, stream);
-    if (e == cudaSuccess)
-        e = cudaMemcpyAsync(csrColInd, keysOut, sizeof(int) * (size_t)nnz, cudaMemcpyDeviceToDevice, stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(P, valsOut, sizeof(int) * (size_t)nnz, cudaMemcpyDeviceToDevice, stream);
+    CsrsortPackKernel<<<WarpRowBlocks(m), 256, 0, stream>>>(csrRowPtr, csrColInd, m, b, keys);
+    b200sp_note_launches(1);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = b200sp_segsort::Sort(csrRowPtr, b, m, keys, scratch, list, stream);
+    if (e == cudaSuccess) {
+        // the merge scratch is free again: its first half takes the permuted P until it is copied over P
+        int *permuted = reinterpret_cast<int *>(scratch);
+        CsrsortUnpackKernel<<<WarpRowBlocks(m), 256, 0, stream>>>(csrRowPtr, m, b, keys, csrColInd, P, permuted);
+        b200sp_note_launches(1);
+        e = cudaGetLastError();
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(P, permuted, sizeof(int) * (size_t)nnz, cudaMemcpyDeviceToDevice, stream);
+    }
     if (e != cudaSuccess) {
         B200SP_LOGE("aclsparseXcsrsort: sort failed (%s)", cudaGetErrorString(e));
         (void)cudaGetLastError();

@@ -63,7 +63,8 @@ def test_coo2csr_feeds_spmv(pkg, handle, device, oracle):
 
 @pytest.mark.parametrize("base", [0, 1])
 @pytest.mark.parametrize("m,n,mean_len,dups", [(1, 1, 1, False), (50, 40, 12, True), (3000, 5000, 30, False),
-                                                (200, 100000, 3000, False), (20000, 300, 4, True), (64, 64, 0, False)])
+                                                (200, 100000, 3000, False), (20000, 300, 4, True), (64, 64, 0, False),
+                                                (3, 200000, 70000, False), (5, 50, 9000, True)])
 def test_csrsort(pkg, handle, device, oracle, m, n, mean_len, dups, base):
     from ctypes import byref, c_size_t, c_void_p
     L = pkg.lib()
@@ -297,3 +298,36 @@ def test_fixtures_of_the_reference_goldens(pkg, handle, device, golden_dir):
             assert np.array_equal(o_cp.cpu().numpy(), z[f"{k}/col_ptr"]), k
             assert np.array_equal(o_ri.cpu().numpy()[:nnz], z[f"{k}/row_ind"]), k
             assert np.array_equal(o_v.cpu().numpy()[:nnz].view(np.uint32), z[f"{k}/val_out"]), k
+
+
+def test_csr2csc_hot_columns(pkg, handle, device, oracle):
+    """Columns that almost every row touches: their segments (9000 and 5000 entries) are longer than one
+    shared-memory chunk of the sort, so the chunk sort + merge passes run, with a run left over."""
+    from ctypes import byref, c_size_t, c_void_p
+    L, S = pkg.lib(), pkg
+    rng = np.random.default_rng(77)
+    m, n = 9000, 400
+    rows = []
+    for r in range(m):
+        extra = rng.choice(np.arange(2, n), size=int(rng.integers(0, 4)), replace=False)
+        cols = np.concatenate([[0], [1] if r % 9 < 5 else [], extra]).astype(np.int32)
+        rows.append(np.sort(cols))
+    rp = np.zeros(m + 1, np.int32)
+    rp[1:] = np.cumsum([c.size for c in rows])
+    ci = np.concatenate(rows).astype(np.int32)
+    val = rng.integers(0, 1 << 30, size=ci.size).astype(np.uint32)
+    want_cp, want_ri, want_v = oracle.csr2csc(m, n, rp, ci, val, 0)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    P = lambda t: c_void_p(t.data_ptr())
+    d_rp, d_ci, d_v = dev(rp), dev(ci), dev(val.view(np.int32))
+    o_v, o_ri = torch.zeros_like(d_v), torch.zeros_like(d_ci)
+    o_cp = torch.zeros(n + 1, dtype=torch.int32, device=device)
+    size = c_size_t()
+    assert L.aclsparseCsr2cscEx2_bufferSize(handle.raw, m, n, ci.size, None, None, None, None, None, None, S.ACL_FLOAT, 1,
+                                            0, 0, byref(size)) == 0
+    buf = torch.empty(size.value, dtype=torch.uint8, device=device)
+    assert L.aclsparseCsr2cscEx2(handle.raw, m, n, ci.size, P(d_v), P(d_rp), P(d_ci), P(o_v), P(o_cp), P(o_ri),
+                                 S.ACL_FLOAT, 1, 0, 0, P(buf)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(o_cp.cpu().numpy(), want_cp) and np.array_equal(o_ri.cpu().numpy(), want_ri)
+    assert np.array_equal(o_v.cpu().numpy().view(np.uint32), want_v)
