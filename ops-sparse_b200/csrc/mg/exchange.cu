@@ -69,9 +69,9 @@ __global__ void __launch_bounds__(256) MgPushKernel(PeerTable peers, int rank, i
     }
     Control *mine = reinterpret_cast<Control *>(peers.base[rank]);
     __shared__ int sLast;
-    __threadfence_system();  // this thread's stores are visible system-wide before the arrival below
-    __syncthreads();
+    __syncthreads();  // every thread of the CTA has issued its stores ...
     if (threadIdx.x == 0) {
+        __threadfence_system();  // ... and this fence, ordered after them by the barrier, makes them visible system-wide
         const uint32_t old = atomicAdd(&mine->arrived, 1u);
         sLast = (old == gridDim.x - 1);
         if (sLast) mine->arrived = 0;  // ready for the next launch

@@ -81,6 +81,16 @@ inline size_t AlignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 #endif
 constexpr int kLongLen = B200SP_SPMV_LONG_LEN;
 
+// Long rows that keep CTAs of their own (the list path) are cut into segments of kSegLen entries, a CTA each: a
+// 16384-entry row is then eight CTAs working side by side instead of one CTA making eight round trips to memory,
+// which is what bounded a product on a small shard.  A row of several segments is finished by whichever of its
+// CTAs arrives last: it adds the segments' partial sums in segment order (no wait, fixed order).
+#ifndef B200SP_SPMV_SEG_LEN
+#define B200SP_SPMV_SEG_LEN 2048
+#endif
+constexpr int kSegLen = B200SP_SPMV_SEG_LEN;
+
+
 struct PlanLayout {  // tile plan: what SpmvTileKernel needs
     int64_t ntiles;
     size_t offTileRow, offCounters, offHead, offTail, total;
@@ -425,6 +435,7 @@ struct BinHeader {  // first 256 bytes of the binned plan
     unsigned long long shortNnz;  // entries in short rows (picks the lane-group width)
     int32_t shortRows;
     int32_t unsorted;         // set when a long row has descending column indices
+    int32_t segments;         // segments the long rows were cut into
 };
 
 // Long rows, second form: x is cut into blocks of kXBlockElems columns and every CTA of
@@ -517,6 +528,53 @@ __global__ void __launch_bounds__(1024) SpmvSortByLengthKernel(const int32_t *__
         const int4 ent = in[i];
         out[atomicAdd(&sHist[lengthClass(ent)], 1)] = ent;
     }
+}
+
+// One CTA: segment table of the ordered long list.  Slot i (row r, entries [s, e)) gets ceil(len / kSegLen)
+// consecutive entries {r, segment start, segment end, i} of `segs`, rowSeg[i] = {first partial slot, segments}, and
+// a zeroed arrival counter; the order of `segs` is the order of the list (longest rows first).
+__global__ void __launch_bounds__(1024) SpmvCutSegmentsKernel(BinHeader *hdr, const int4 *__restrict__ listL,
+                                                               int4 *__restrict__ segs, int2 *__restrict__ rowSeg,
+                                                               int32_t *__restrict__ counters)
+{
+    __shared__ int sWarp[32];
+    __shared__ int sCarry;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = hdr->longs;
+    if (tid == 0) sCarry = 0;
+    __syncthreads();
+    for (int i0 = 0; i0 < n; i0 += 1024) {
+        const int i = i0 + tid;
+        int4 ent = make_int4(0, 0, 0, 0);
+        int nseg = 0;
+        if (i < n) {
+            ent = listL[i];
+            nseg = (ent.z - ent.y + kSegLen - 1) / kSegLen;
+        }
+        int incl = nseg;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) sWarp[warp] = incl;
+        __syncthreads();
+        int before = sCarry;
+        for (int w = 0; w < warp; ++w) before += sWarp[w];
+        const int first = before + incl - nseg;
+        if (i < n) {
+            rowSeg[i] = make_int2(first, nseg);
+            counters[i] = 0;
+            for (int k = 0; k < nseg; ++k) {
+                const int a = ent.y + k * kSegLen;
+                segs[first + k] = make_int4(ent.x, a, a + kSegLen < ent.z ? a + kSegLen : ent.z, i);
+            }
+        }
+        __syncthreads();
+        if (tid == 1023) sCarry = before + incl;
+        __syncthreads();
+    }
+    if (tid == 0) hdr->segments = sCarry;
 }
 
 // One warp per listed long row: checks that its column indices ascend, then cuts it at the x
@@ -788,18 +846,27 @@ __device__ __forceinline__ void MediumRowsBody(unsigned bid, const int32_t *__re
     }
 }
 
+struct LongSegs {             // the long rows cut into segments (see SpmvCutSegmentsKernel)
+    const int4 *segs;         // {row, start, end, slot}
+    const int4 *list;         // {row, row start, row end, 0} per slot
+    const int2 *rowSeg;       // {first partial slot, segments} per slot
+    int32_t *counters;        // arrivals per slot
+    void *partials;           // one compute-type value per segment
+};
+
 template <typename CompT, typename ValT, typename OutT, bool kVec, int kUnrollQ = kLongUnroll>
 __device__ __forceinline__ void LongRowBody(unsigned bid, const int32_t *__restrict__ colInd,
                                             const ValT *__restrict__ val, const ValT *__restrict__ x,
-                                            OutT *__restrict__ y, const int4 *__restrict__ list,
-                                            const Scalars<CompT> &sc, CompT *sWarp)
+                                            OutT *__restrict__ y, const LongSegs &ls, const Scalars<CompT> &sc,
+                                            CompT *sWarp)
 {
     const int tid = threadIdx.x;
-    const int4 ent = __ldg(list + bid);
-    const int r = ent.x, s = ent.y, e = ent.z;
+    const int4 ent = __ldg(ls.segs + bid);
+    const int r = ent.x, s = ent.y, e = ent.z, slot = ent.w;
+    const int2 rs = __ldg(ls.rowSeg + slot);  // {first partial slot, segments of this row}
     const CompT beta = sc.Beta();
     CompT yOld = CompT(0);
-    if (tid == 0 && beta != CompT(0)) yOld = Widen<CompT>(y[r]);  // requested now, used at the end
+    if (tid == 0 && rs.y == 1 && beta != CompT(0)) yOld = Widen<CompT>(y[r]);  // requested now, used at the end
     CompT sum = CompT(0);
     if (kVec) {
         // whole aligned quads [vs, ve); up to three single entries before and after them
@@ -847,6 +914,20 @@ __device__ __forceinline__ void LongRowBody(unsigned bid, const int32_t *__restr
         CompT tot = CompT(0);
 #pragma unroll
         for (int w = 0; w < 8; ++w) tot += sWarp[w];
+        if (rs.y > 1) {
+            // one of several segments: leave the partial sum, and finish the row if this CTA is the last to arrive
+            CompT *part = static_cast<CompT *>(ls.partials) + rs.x;
+            const int rowStart = __ldg(ls.list + slot).y;
+            part[(s - rowStart) / kSegLen] = tot;
+            __threadfence();
+            const int old = atomicAdd(ls.counters + slot, 1);
+            if (old != rs.y - 1) return;
+            ls.counters[slot] = 0;  // ready for the next launch
+            __threadfence();
+            tot = CompT(0);
+            for (int k = 0; k < rs.y; ++k) tot += __ldcg(part + k);  // segment order: the sum does not depend on timing
+            if (beta != CompT(0)) yOld = Widen<CompT>(y[r]);
+        }
         CompT z = sc.Alpha() * tot;
         if (beta != CompT(0)) z += beta * yOld;
         y[r] = Narrow<OutT>(z);
@@ -885,10 +966,10 @@ template <typename CompT, typename ValT, typename OutT, bool kVec>
 __global__ void __launch_bounds__(256) SpmvLongListKernel(const int32_t *__restrict__ colInd,
                                                            const ValT *__restrict__ val,
                                                            const ValT *__restrict__ x, OutT *__restrict__ y,
-                                                           const int4 *__restrict__ list, Scalars<CompT> sc)
+                                                           LongSegs ls, Scalars<CompT> sc)
 {
     __shared__ CompT sWarp[8];
-    LongRowBody<CompT, ValT, OutT, kVec>(blockIdx.x, colInd, val, x, y, list, sc, sWarp);
+    LongRowBody<CompT, ValT, OutT, kVec>(blockIdx.x, colInd, val, x, y, ls, sc, sWarp);
 }
 
 // All three bins in one grid, for matrices whose long rows keep a CTA each: blocks [0, nL) take one long
@@ -900,13 +981,13 @@ __global__ void __launch_bounds__(256, 6) SpmvAllBinsKernel(const int32_t *__res
                                                              const int32_t *__restrict__ colInd,
                                                              const ValT *__restrict__ val, const ValT *__restrict__ x,
                                                              OutT *__restrict__ y, const int4 *__restrict__ listM,
-                                                             const int4 *__restrict__ listL, int nM, int nL, int rows,
+                                                             LongSegs ls, int nM, int nL, int rows,
                                                              Scalars<CompT> sc)
 {
     __shared__ CompT sWarp[8];
     unsigned b = blockIdx.x;
-    if (b < (unsigned)nL) {
-        LongRowBody<CompT, ValT, OutT, kVec, 2>(b, colInd, val, x, y, listL, sc, sWarp);
+    if (b < (unsigned)nL) {  // nL counts segments here
+        LongRowBody<CompT, ValT, OutT, kVec, 2>(b, colInd, val, x, y, ls, sc, sWarp);
         return;
     }
     b -= (unsigned)nL;
@@ -1092,9 +1173,10 @@ int GroupWidthFor(int64_t rows, int64_t nnz)
 // Binned plan in the caller's buffer: header, list of medium rows, list of long rows and, when
 // the matrix is narrow enough for the blocked long-row kernel, that kernel's tables.
 struct BinLayout {
-    int64_t capM, capL;
+    int64_t capM, capL, capS;
     int32_t xBlocks;  // column blocks of x; 0 = the blocked long-row kernel is not available
-    size_t offHeader, offListM, offListL, offTmpL, offSegStart, offLongCounters, offPartials, total;
+    size_t offHeader, offListM, offListL, offTmpL, offSegStart, offLongCounters, offPartials, offSegs, offRowSeg,
+        offSegCounters, offSegPartials, total;
 };
 
 inline BinLayout BinLayoutFor(int64_t rows, int64_t cols, int64_t nnz)
@@ -1112,12 +1194,18 @@ inline BinLayout BinLayoutFor(int64_t rows, int64_t cols, int64_t nnz)
     L.offSegStart = AlignUp(L.offTmpL + sizeof(int4) * (size_t)L.capL, 256);
     L.offLongCounters = AlignUp(L.offSegStart + sizeof(int32_t) * (size_t)L.capL * (L.xBlocks > 0 ? L.xBlocks + 1 : 0), 256);
     L.offPartials = AlignUp(L.offLongCounters + sizeof(int32_t) * kMaxLongGroups, 256);
-    L.total = AlignUp(L.offPartials + 4 * (size_t)L.capL * L.xBlocks, 256);
+    L.capS = nnz / kSegLen + L.capL;  // a row of len entries has at most len / kSegLen + 1 segments
+    L.offSegs = AlignUp(L.offPartials + 4 * (size_t)L.capL * L.xBlocks, 256);
+    L.offRowSeg = AlignUp(L.offSegs + sizeof(int4) * (size_t)L.capS, 256);
+    L.offSegCounters = AlignUp(L.offRowSeg + sizeof(int2) * (size_t)L.capL, 256);
+    L.offSegPartials = AlignUp(L.offSegCounters + sizeof(int32_t) * (size_t)L.capL, 256);
+    L.total = AlignUp(L.offSegPartials + 4 * (size_t)L.capS, 256);
     return L;
 }
 
 // plan_info layout shared with the host layer (see b200sp_kernels.h)
-enum { kInfoKind = 0, kInfoMedium = 1, kInfoLong = 2, kInfoGroup = 3, kInfoXBlocks = 4, kInfoBlockElems = 5, kInfoLongLen = 6 };
+enum { kInfoKind = 0, kInfoMedium = 1, kInfoLong = 2, kInfoGroup = 3, kInfoXBlocks = 4, kInfoBlockElems = 5, kInfoLongLen = 6,
+       kInfoSegments = 7 };
 enum { kPlanTiles = 0, kPlanBinned = 1, kPlanBinnedBlocked = 2 };  // blocked: long rows go to SpmvLongBlockKernel
 
 template <typename CompT, typename ValT, typename OutT, bool kVec>
@@ -1147,7 +1235,13 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
     char *p = static_cast<char *>(plan);
     const int4 *listM = reinterpret_cast<const int4 *>(p + L.offListM);
     const int4 *listL = reinterpret_cast<const int4 *>(p + L.offListL);
-    const int nM = info[kInfoMedium], nL = info[kInfoLong], G = info[kInfoGroup];
+    const int nM = info[kInfoMedium], nL = info[kInfoLong], G = info[kInfoGroup], nS = info[kInfoSegments];
+    LongSegs ls;
+    ls.segs = reinterpret_cast<const int4 *>(p + L.offSegs);
+    ls.list = listL;
+    ls.rowSeg = reinterpret_cast<const int2 *>(p + L.offRowSeg);
+    ls.counters = reinterpret_cast<int32_t *>(p + L.offSegCounters);
+    ls.partials = p + L.offSegPartials;
     const bool vec = (reinterpret_cast<uintptr_t>(colInd) % 16 == 0) &&
                      (reinterpret_cast<uintptr_t>(val) % (4 * sizeof(ValT)) == 0);
 #if B200SP_SPMV_FUSE_LIST
@@ -1155,12 +1249,12 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
     // keep two kernels on forked streams -- equal in isolation (36.9 us either way on 7.6 M entries), but four
     // such products pipelined on three streams with their host copies took 329 us fused against 287 us forked.
     if (nL > 0 && nnz <= (4ll << 20) && !(info[kInfoKind] == kPlanBinnedBlocked && L.xBlocks > 0)) {
-        const unsigned blocks = (unsigned)nL + (unsigned)((nM + 7) / 8) + (unsigned)((rows * G + 255) / 256);
+        const unsigned blocks = (unsigned)nS + (unsigned)((nM + 7) / 8) + (unsigned)((rows * G + 255) / 256);
         auto launch = [&]<int GG>() {
             if (vec) SpmvAllBinsKernel<CompT, ValT, OutT, GG, true><<<blocks, 256, 0, stream>>>(
-                rowPtr, colInd, val, x, y, listM, listL, nM, nL, (int)rows, sc);
+                rowPtr, colInd, val, x, y, listM, ls, nM, nS, (int)rows, sc);
             else SpmvAllBinsKernel<CompT, ValT, OutT, GG, false><<<blocks, 256, 0, stream>>>(
-                rowPtr, colInd, val, x, y, listM, listL, nM, nL, (int)rows, sc);
+                rowPtr, colInd, val, x, y, listM, ls, nM, nS, (int)rows, sc);
         };
         switch (G) {
             case 2: launch.template operator()<2>(); break;
@@ -1208,8 +1302,8 @@ int LaunchBinned(const int32_t *rowPtr, const int32_t *colInd, const ValT *val, 
                                 : LaunchLongBlock<CompT, ValT, OutT, false>(la, L.xBlocks * groups, sL);
             if (rcL != 0) return rcL;
         } else {
-            if (vec) SpmvLongListKernel<CompT, ValT, OutT, true><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
-            else SpmvLongListKernel<CompT, ValT, OutT, false><<<(unsigned)nL, 256, 0, sL>>>(colInd, val, x, y, listL, sc);
+            if (vec) SpmvLongListKernel<CompT, ValT, OutT, true><<<(unsigned)nS, 256, 0, sL>>>(colInd, val, x, y, ls, sc);
+            else SpmvLongListKernel<CompT, ValT, OutT, false><<<(unsigned)nS, 256, 0, sL>>>(colInd, val, x, y, ls, sc);
             b200sp_note_launches(1);
         }
         if (lanes != nullptr) cudaEventRecord(lanes->join[0], sL);
@@ -1422,7 +1516,11 @@ int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t 
             reinterpret_cast<int4 *>(p + L.offTmpL));
         SpmvSortByLengthKernel<<<1, 1024, 0, st>>>(&hdr->longs, reinterpret_cast<const int4 *>(p + L.offTmpL),
                                                    reinterpret_cast<int4 *>(p + L.offListL));
-        b200sp_note_launches(2);
+        SpmvCutSegmentsKernel<<<1, 1024, 0, st>>>(hdr, reinterpret_cast<const int4 *>(p + L.offListL),
+                                                  reinterpret_cast<int4 *>(p + L.offSegs),
+                                                  reinterpret_cast<int2 *>(p + L.offRowSeg),
+                                                  reinterpret_cast<int32_t *>(p + L.offSegCounters));
+        b200sp_note_launches(3);
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
@@ -1450,7 +1548,7 @@ int b200sp_spmv_analyze(const int32_t *row_ptr, const int32_t *col_ind, int64_t 
     plan_info[kInfoXBlocks] = useBlocked ? L.xBlocks : 0;
     plan_info[kInfoBlockElems] = useBlocked ? kXBlockElems : 0;
     plan_info[kInfoLongLen] = kLongLen;
-    plan_info[7] = 0;
+    plan_info[kInfoSegments] = host.segments;
     plan_info[kInfoMedium] = host.medium;
     plan_info[kInfoLong] = host.longs;
 #ifdef B200SP_SPMV_FORCE_SHORT_G

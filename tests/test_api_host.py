@@ -191,14 +191,17 @@ def test_buffer_size_formulas(pkg):
     assert 16 * tiles <= tile_plan <= 16 * tiles + 4096   # tile table + counters + two partial arrays, 4 B each
     # binned plan: a list entry per row that can be longer than 32 entries, one per possible long row (512+)
     # {row, start, end, -} per entry; the long list twice (as found, then ordered by length)
-    long_len = 512
-    bins = 256 + 16 * (min(rows, nnz // 33) + 1) + 2 * 16 * (nnz // long_len + 1)
+    long_len, seg_len = 512, 2048
+    cap_long = nnz // long_len + 1
+    cap_segs = nnz // seg_len + cap_long   # long rows cut into 2048-entry segments: {row, start, end, slot} each
+    bins = 256 + 16 * (min(rows, nnz // 33) + 1) + 2 * 16 * cap_long
+    segs = 16 * cap_segs + 8 * cap_long + 4 * cap_long + 4 * cap_segs  # + per-row {first, count}, counters, partial sums
     # too wide for the blocked long-row kernel (more than 64 blocks of 32768 columns): the lists only
-    assert max(tile_plan, bins) <= L.b200sp_spmv_plan_bytes(rows, 1 << 22, nnz) <= max(tile_plan, bins) + 1024
+    assert max(tile_plan, bins + segs) <= L.b200sp_spmv_plan_bytes(rows, 1 << 22, nnz) <= max(tile_plan, bins + segs) + 4096
     # narrow enough: per possible long row, xBlocks + 1 cut points and xBlocks partial sums, 4 B each
     xb = (rows + 32767) // 32768
-    blocked = bins + (nnz // long_len + 1) * (2 * xb + 1) * 4 + 256
-    assert blocked <= L.b200sp_spmv_plan_bytes(rows, rows, nnz) <= blocked + 2048
+    blocked = bins + segs + cap_long * (2 * xb + 1) * 4 + 256
+    assert blocked <= L.b200sp_spmv_plan_bytes(rows, rows, nnz) <= blocked + 4096
     assert L.b200sp_spmm_plan_bytes(1 << 18, 1 << 24, 64) >= 2 * ((1 << 24) // 4096) * 64 * 4
 
 
