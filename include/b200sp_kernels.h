@@ -189,9 +189,18 @@ int b200sp_spmm_launch(const int32_t *row_ptr, const int32_t *col_ind, const voi
                        void *plan, int32_t segments, void *stream);
 
 /* 1 when a wait on the copy engine ran out of time in the SpMM row-stream kernel since the library was
- * loaded (the affected rows of C were then not written), 0 when none did, -1 when the flag cannot be
- * read.  Synchronises the device. */
+ * loaded or the flag was last cleared (the affected rows of C were then not written), 0 when none did, -1 when
+ * the flag cannot be read.  Synchronises the device.  Callers that need certainty poll it after synchronising. */
 int b200sp_spmm_stream_error(void);
+/* Clears that flag (synchronises the device).  aclsparseSpMMPreprocess also reads and clears it and returns
+ * ACL_SPARSE_STATUS_EXECUTION_FAILED when it was set: a caller that never polls still learns of a product that
+ * was cut short at its next analysis. */
+int b200sp_spmm_stream_error_clear(void);
+/* For tests of that path: later row-stream launches wait at most wait_cycles SM clocks on a copy barrier
+ * (0 = the default, about a second) and expect extra_tx bytes more than they copy on every barrier, so that with
+ * extra_tx > 0 every wait runs out: the kernel must set the flag, stop writing C and return.  (0, 0) restores the
+ * normal behaviour.  Not thread-safe; nothing faults or hangs in either setting. */
+void b200sp_spmm_stream_wait_test(long long wait_cycles, unsigned extra_tx);
 
 /* Number of streaming multiprocessors of the current device (cached after the first call). */
 int b200sp_sm_count(void);

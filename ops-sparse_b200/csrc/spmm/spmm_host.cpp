@@ -103,6 +103,13 @@ aclsparseStatus_t aclsparseSpMMPreprocess(aclsparseHandle_t handle, aclsparseOpe
     const aclsparseStatus_t an =
         Analyse(matA, matC->cols, buffer, handle != nullptr ? handle->stream : nullptr, &segments);
     if (an != ACL_SPARSE_STATUS_SUCCESS) return an;
+    // The analysis has just synchronised: the one place on this path where a row-stream product that gave up on a
+    // copy (see b200sp_spmm_stream_error) can be reported without adding a synchronisation to a compute call.
+    if (b200sp_spmm_stream_error() == 1) {
+        (void)b200sp_spmm_stream_error_clear();
+        B200SP_LOGE("aclsparseSpMMPreprocess: an earlier aclsparseSpMM gave up waiting for a copy; its C is incomplete");
+        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+    }
     ActivePlan p;
     p.buffer = buffer;
     p.kind = PlanKind::kSpmm;

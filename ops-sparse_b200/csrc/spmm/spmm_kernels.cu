@@ -516,6 +516,10 @@ constexpr int kStreamWarps = B200SP_SPMM_STREAM_WARPS;
 constexpr int kStreamThreads = kStreamWarps * 32;
 constexpr int kStreamRows = 32;                              // rows of A per warp
 constexpr long long kStreamWaitCycles = 1ll << 31;           // SM clocks (about a second) to wait on one barrier before giving up
+// What the next launches pass to the kernel as its wait limit and as bytes to expect beyond those it copies
+// (b200sp_spmm_stream_wait_test: a test makes a wait run out without any fault by expecting bytes nobody sends).
+long long gHostStreamWaitCycles = kStreamWaitCycles;
+unsigned gHostStreamExtraTx = 0;
 
 __device__ int gStreamError;  // set when a wait ran out (never observed; the kernel then stops writing C)
 
@@ -541,12 +545,12 @@ __device__ __forceinline__ bool MbarTryWait(uint64_t *bar, uint32_t parity)
     return ok != 0;
 }
 // Polls with a time limit; false when the limit was reached.
-__device__ __forceinline__ bool MbarWait(uint64_t *bar, uint32_t parity)
+__device__ __forceinline__ bool MbarWait(uint64_t *bar, uint32_t parity, long long limit)
 {
     if (MbarTryWait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!MbarTryWait(bar, parity)) {
-        if (clock64() - t0 > kStreamWaitCycles) return false;
+        if (clock64() - t0 > limit) return false;
     }
     return true;
 }
@@ -654,6 +658,8 @@ struct StreamArgs {
     long long ldb;
     long long ldc;
     ScalarsF sc;
+    long long waitCycles;   // limit of every wait on a copy barrier, in SM clocks
+    unsigned extraTx;       // bytes expected on every barrier beyond those copied (0 outside the wait test)
 };
 
 template <int kRowBytes> struct StreamShape {
@@ -756,7 +762,7 @@ __global__ void __launch_bounds__(kStreamThreads) SpmmRowStreamKernel(const Stre
     auto issueBatch = [&](int k) {
         const int buf = k % kStreamBuffers;
         const int live = total - k * kBatch < kBatch ? total - k * kBatch : kBatch;
-        if (lane == 0) MbarExpectTx(sBar + buf, (uint32_t)live * kRowBytes);
+        if (lane == 0) MbarExpectTx(sBar + buf, (uint32_t)live * kRowBytes + a.extraTx);
         __syncwarp();
         if (lane < live) {
             sVal[buf * kBatch + lane] = eVal;
@@ -786,7 +792,7 @@ __global__ void __launch_bounds__(kStreamThreads) SpmmRowStreamKernel(const Stre
         if (k + ahead + 1 < nBatches) fetchEntries(k + ahead + 1);  // lands while this batch is summed
         const int buf = k % kStreamBuffers;
         __syncwarp();
-        if (!MbarWait(sBar + buf, (uint32_t)(k / kStreamBuffers) & 1u)) {
+        if (!MbarWait(sBar + buf, (uint32_t)(k / kStreamBuffers) & 1u, a.waitCycles)) {
             failedAt = k;
             if (lane == 0) atomicExch(&gStreamError, 1);
             break;
@@ -819,7 +825,7 @@ __global__ void __launch_bounds__(kStreamThreads) SpmmRowStreamKernel(const Stre
         // failedAt .. failedAt + ahead) a bounded chance to land before the shared memory they
         // target is released.
         for (int k = failedAt; k <= failedAt + ahead && k < nBatches; ++k)
-            (void)MbarWait(sBar + k % kStreamBuffers, (uint32_t)(k / kStreamBuffers) & 1u);
+            (void)MbarWait(sBar + k % kStreamBuffers, (uint32_t)(k / kStreamBuffers) & 1u, a.waitCycles);
     }
 }
 
@@ -1017,6 +1023,8 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
             sa.ldb = sh->ldb;
             sa.ldc = sh->ldc;
             sa.sc = a.sc;
+            sa.waitCycles = gHostStreamWaitCycles;
+            sa.extraTx = gHostStreamExtraTx;
             const int rc = rowBytes == 512 ? LaunchRowStream<ValT, OutT, 512>(sa, stream)
                                            : LaunchRowStream<ValT, OutT, 1024>(sa, stream);
             if (rc != 0) return rc;
@@ -1050,6 +1058,18 @@ int b200sp_spmm_stream_error(void)
     int flag = 0;
     if (cudaMemcpyFromSymbol(&flag, gStreamError, sizeof(flag)) != cudaSuccess) return -1;
     return flag;
+}
+
+int b200sp_spmm_stream_error_clear(void)
+{
+    const int zero = 0;
+    return (int)cudaMemcpyToSymbol(gStreamError, &zero, sizeof(zero));
+}
+
+void b200sp_spmm_stream_wait_test(long long wait_cycles, unsigned extra_tx)
+{
+    gHostStreamWaitCycles = wait_cycles > 0 ? wait_cycles : kStreamWaitCycles;
+    gHostStreamExtraTx = extra_tx;
 }
 
 size_t b200sp_spmm_plan_bytes(int64_t rows, int64_t nnz, int64_t n) { return LayoutFor(rows, nnz, n).total; }

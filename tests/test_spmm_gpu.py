@@ -311,6 +311,51 @@ def test_status_codes(handle, device, pkg):
     assert torch.all(C.values == 7.0)
 
 
+def test_row_stream_wait_that_runs_out(pkg, handle, device, oracle):
+    """Failure detection without a fault: the row-stream kernel is told to expect 16 bytes more than it copies on
+    every barrier and to wait two milliseconds at most.  Every wait runs out; the kernel must raise the flag,
+    write nothing of C (beta = 1 leaves the rows without entries as they were) and return with the GPU usable;
+    the next Preprocess reports it; with the normal settings the same product is correct again."""
+    from ops_sparse_b200 import api, synth
+    L = pkg.lib()
+    L.b200sp_spmm_stream_wait_test.argtypes = [ctypes.c_longlong, ctypes.c_uint]
+    L.b200sp_spmm_stream_wait_test.restype = None
+    rng = np.random.default_rng(41)
+    m, k, n = 3000, 2500, 256
+    lengths = synth.zipf_lengths(rng, m, 1.9, 900, 10.0)   # rows of up to 900 entries: the row-stream kernel alone
+    lengths[rng.random(m) < 0.2] = 0
+    A = synth.csr_from_lengths(rng, lengths, k, synth.uniform)
+    Bq = torch.from_numpy(rng.standard_normal((k, n)).astype(np.float32)).to(torch.bfloat16)
+    C0 = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32))
+    dA = api.CsrMatrix(torch.from_numpy(A.row_ptr).to(device), torch.from_numpy(A.col_ind).to(device),
+                       torch.from_numpy(A.values).to(device).to(torch.bfloat16), m, k)
+    dB, dC = api.DnMat.row_major(Bq.to(device)), api.DnMat.row_major(C0.to(device))
+    buf = api.spmm_preprocess(handle, dA, dB, dC)
+    torch.cuda.synchronize()
+    assert L.b200sp_spmm_stream_error() == 0
+    try:
+        L.b200sp_spmm_stream_wait_test(1 << 22, 16)
+        api.spmm(handle, dA, dB, dC, 1.0, 1.0, buffer=buf)
+        torch.cuda.synchronize()                              # returns: nothing hangs
+        assert L.b200sp_spmm_stream_error() == 1
+        assert torch.equal(dC.values.cpu(), C0)               # not one row of C was written with a partial sum
+    finally:
+        L.b200sp_spmm_stream_wait_test(0, 0)
+    # the failure surfaces at the next synchronising entry point, once
+    from ops_sparse_b200 import ACL_FLOAT
+    args = (handle.raw, 0, 0, None, dA.raw, dB.raw, None, dC.raw, ACL_FLOAT, 0, api._ptr(buf))
+    assert L.aclsparseSpMMPreprocess(*args) == pkg.ACL_SPARSE_STATUS_EXECUTION_FAILED
+    assert L.b200sp_spmm_stream_error() == 0
+    assert L.aclsparseSpMMPreprocess(*args) == 0
+    api.spmm(handle, dA, dB, dC, 1.0, 1.0, buffer=buf)
+    torch.cuda.synchronize()
+    assert L.b200sp_spmm_stream_error() == 0
+    vw = torch.from_numpy(A.values).to(torch.bfloat16).to(torch.float32).numpy()
+    bad, worst = oracle.check_spmm_f32(A.row_ptr, A.col_ind, vw, Bq.to(torch.float32).numpy(), C0.numpy(),
+                                       dC.values.cpu().numpy(), 1.0, 1.0, 2e-3)
+    assert bad == 0, worst
+
+
 def test_no_wait_ran_out_in_the_row_stream_kernel(pkg, device):
     """The row-stream kernel bounds its waits on the copy engine and raises a flag when one runs out;
     after everything above it must still be clear.  (Runs last in this file.)"""
