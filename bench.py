@@ -284,11 +284,11 @@ def config_list(args, world: int) -> list[str]:
 # the kernels of one product), with the summary under profiles/ they were read from.  A figure is attached to a
 # line only when the kernels that ran are the ones the capture covers.
 NCU_TRAFFIC = {
-    "c2": {"bytes": 287_100_000, "kernels": "SpmvLongBlockKernel + SpmvMediumShortKernel",
+    "c2": {"bytes": 281_200_000, "kernels": "SpmvLongBlockKernel + SpmvMediumShortKernel",
            "source": "profiles/spmv_binned_c2_powerlaw_f32.md"},
-    "c3": {"bytes": 353_516_032, "kernels": "SpmvShortRowsKernel", "source": "profiles/spmv_binned_c3_stencil27_f16.md"},
-    "c4": {"bytes": 641_619_968, "kernels": "SpmmFastKernel", "source": "profiles/spmm_fast_c4_f32_n64.md"},
-    "c5": {"bytes": 18_800_000_000, "kernels": "SpmmRowStreamKernel + SpmmFastKernel",
+    "c3": {"bytes": 352_300_000, "kernels": "SpmvShortRowsKernel", "source": "profiles/spmv_binned_c3_stencil27_f16.md"},
+    "c4": {"bytes": 635_600_000, "kernels": "SpmmFastKernel", "source": "profiles/spmm_fast_c4_f32_n64.md"},
+    "c5": {"bytes": 18_340_000_000, "kernels": "SpmmRowStreamKernel + SpmmFastKernel",
            "source": "profiles/spmm_rowstream_c5_bf16_n256.md"},
 }
 # What the counters show to be the busy resource where it is not DRAM.
@@ -709,6 +709,28 @@ def aux_arm(args, synth, oracle):
                     "workspace_bytes": int(size.value)}
         kernels = ("ColumnHistogramKernel + Scan{BlockSums,Sums,Apply}Kernel + ScatterKeysKernel + SegSort{Short,Long}Kernel"
                    " + GatherKernel")
+    elif args.op in ("spmvop-alg1", "spmvop-alg2"):
+        # the SpMVOp plan API (compensated row sums) on the c2 matrix, Z aliasing Y
+        cfg = synth.config2()
+        A = cfg["A"]
+        m, n, nnz = A.rows, A.cols, A.nnz
+        d_rp, d_ci, d_v = to(A.row_ptr), to(A.col_ind), to(A.values)
+        dA = api.CsrMatrix(d_rp, d_ci, d_v, m, n)
+        y0 = to(cfg["y"])
+        dx, dy = api.DnVec(to(cfg["x"])), api.DnVec(y0.clone())
+        plan = api.SpMVOpPlan(h, dA, dx, dy, dy, alg=2 if args.op.endswith("2") else 1)
+        fn = lambda: plan.run(dx, dy, dy, cfg["alpha"], cfg["beta"])
+        t = timed(fn, lambda: dy.values.copy_(y0))
+        t0 = time.perf_counter()
+        gold = oracle.spmv_op(A.row_ptr, A.col_ind, A.values, cfg["x"], cfg["y"], cfg["alpha"], cfg["beta"])
+        cpu_s = time.perf_counter() - t0
+        got = dy.values.cpu().numpy().astype(np.float64)
+        scale = abs(cfg["alpha"]) * oracle.spmv_abs_rowsum(A.row_ptr, A.col_ind, A.values, cfg["x"]) + np.abs(cfg["beta"] * cfg["y"])
+        ok = bool(np.all(np.abs(got - gold.astype(np.float64)) <= 1e-6 * scale + 1e-30))
+        alg = synth.algorithmic_bytes_spmv(m, n, nnz, 4, 4, cfg["beta"])
+        workload = {"workload": f"aclsparseSpMVOp ({args.op[-4:]}) on the c2 matrix", "rows": m, "nnz": nnz}
+        kernels = ("SpmvOpLongRowsKernel + SpmvOpRowsKernel per length class" if args.op.endswith("2") else "SpmvOpRowsKernel")
+        plan.close()
     else:  # sddmm: the pattern of a 1 M-node power-law graph, X and Y^T of 256 fp16 per row (the backward of c5's layer)
         cfg = synth.config5(rows=1 << 20)
         A = cfg["A"]
@@ -759,8 +781,9 @@ def aux_arm(args, synth, oracle):
             "cpu_baseline": {"value": cpu_s * 1e3, "unit": "ms", "cores": 1, "kind": "port",
                              "sample": "oracle restatement of the reference golden, one pass on one thread"
                                        + (" (leading rows, scaled by nnz)" if args.op == "sddmm" else "")},
-            "parity": {"ok": bool(ok), "rule": "bit-exact against the golden restatement" if args.op != "sddmm" else
-                       "mixed tolerance of the reference test frame on the leading 200,000 entries' rows"}}
+            "parity": {"ok": bool(ok), "rule": "mixed tolerance of the reference test frame on the leading 200,000 entries' rows"
+                       if args.op == "sddmm" else "|err| <= 1e-6 * (|alpha| sum |a x| + |beta y|) per row against the restated "
+                       "compensated row sums" if args.op.startswith("spmvop") else "bit-exact against the golden restatement"}}
     print(json.dumps(line))
     h.close()
     if not ok:
@@ -779,7 +802,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU golden timing leg")
     ap.add_argument("--replicate", default="peer", choices=["peer", "nccl-allgather", "nccl-broadcast"],
                     help="how x / B reaches every GPU inside a multi-GPU step (see ops-sparse_b200/mg.py)")
-    ap.add_argument("--op", default="", choices=["", "coo2csr", "csrsort", "csr2csc", "sddmm"],
+    ap.add_argument("--op", default="", choices=["", "coo2csr", "csrsort", "csr2csc", "sddmm", "spmvop-alg1", "spmvop-alg2"],
                     help="measure one of the operators next to the hot path instead (one GPU)")
     ap.add_argument("--no-graph", action="store_true", help="end-to-end leg: issue every step's operations one by one")
     ap.add_argument("--e2e-panels", type=int, default=4,
