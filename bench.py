@@ -386,9 +386,11 @@ def measure_config(name: str, args, env, head: bool) -> dict:
                                         api._ptr(op.buffer), count)
             if rc != 0:
                 raise RuntimeError(f"compute entry point returned status {rc}")
+        elif with_exchange:
+            op.steps(alpha, beta, count)  # the compiled loop again when the peer exchange is in use
         else:
             for _ in range(count):
-                op.step(alpha, beta, broadcast=with_exchange)
+                op.step(alpha, beta, broadcast=False)
 
     def barrier():
         torch.cuda.synchronize()
@@ -590,7 +592,9 @@ def gpu_arm(args, synth, oracle):
                             "exchange to its steady state"),
             "analysis": "aclsparse*Preprocess once, outside the timed region",
             "step_issue": ("compiled loop over the C API (b200spRepeatSpMV / b200spRepeatSpMM)" if env.world == 1
-                           else "Python loop: one exchange launch and one aclsparse call per step"),
+                           else ("compiled loop over the C API (b200spMgRepeatSpMV / b200spMgRepeatSpMM): one exchange "
+                                 "launch and one aclsparse call per step" if args.replicate == "peer"
+                                 else "Python loop: one collective and one aclsparse call per step")),
         }
         for k in ("per_step_ms", "effective_gbs", "algorithmic_bytes_per_step", "roofline", "e2e", "compute_only",
                   "gpu_launches", "kernels_per_step", "clocks", "parity_full", "l2_policy", "cpu_baseline"):

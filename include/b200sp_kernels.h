@@ -171,6 +171,8 @@ typedef struct b200spSpmmShape {
     int32_t order_c;
     int32_t op_b;
     int32_t kahan;      /* 1 = compensated fp32 accumulation */
+    int32_t block_units; /* from b200sp_spmm_analyze_blocks: units of the column-block path, 0 = not in use */
+    int32_t long_rows;  /* from b200sp_spmm_analyze_blocks: rows the analysis listed as long */
 } b200spSpmmShape;
 
 /* Bytes of workspace for the SpMM analysis + long-row partial sums. */
@@ -181,6 +183,16 @@ size_t b200sp_spmm_plan_bytes(int64_t rows, int64_t nnz, int64_t n);
  * the segment count (4 bytes), returned in *segments. */
 int b200sp_spmm_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, int64_t n, void *plan,
                         size_t plan_bytes, int32_t *segments, void *stream);
+
+/* Second, optional analysis pass, after b200sp_spmm_analyze on the same plan: decides whether the long rows are
+ * better summed block by block of B (B much larger than L2, rows of B of `b_row_bytes` >= 512 bytes, every long
+ * row's columns ascending, partial rows within the plan's budget) and, if so, writes every long row's cut
+ * positions and a table of work units into the plan.  Reads col_ind, so the plan then depends on it too.
+ * *block_units = the number of units (0 = keep the segments), *long_rows = the number of long rows.
+ * Synchronises `stream` twice. */
+int b200sp_spmm_analyze_blocks(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols,
+                               int64_t nnz, int64_t n, int64_t b_row_bytes, void *plan, size_t plan_bytes,
+                               int32_t *block_units, int32_t *long_rows, void *stream);
 
 /* C = alpha * A * op(B) + beta * C.  val_type is the type of A and B, out_type of C.
  * `plan` / `segments` come from b200sp_spmm_analyze on the same row_ptr / rows / nnz / n. */

@@ -13,7 +13,7 @@ The directory name contains a hyphen, so load it through `__graft_entry__.load_p
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, byref, c_double, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, byref, c_double, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
@@ -103,6 +103,12 @@ _SIGNATURES = {
     "aclsparseSpMV": [P, c_int, P, P, P, P, P, c_int, c_int, P],
     "b200spRepeatSpMV": [P, c_int, P, P, P, P, P, c_int, c_int, P, c_int],
     "b200spRepeatSpMM": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P, c_int],
+    # exchange, slice, offset, bytes, firstSeq, replicas, waitMask, then the product's arguments with an array of
+    # per-replica dense descriptors, reps
+    "b200spMgRepeatSpMV": [P, P, c_size_t, c_size_t, c_uint32, c_int, c_uint32, P, c_int, P, P, P, P, P, c_int, c_int,
+                           P, c_int],
+    "b200spMgRepeatSpMM": [P, P, c_size_t, c_size_t, c_uint32, c_int, c_uint32, P, c_int, c_int, P, P, P, P, P, c_int,
+                           c_int, P, c_int],
     # SpMM: handle, opA, opB, alpha, matA, matB, beta, matC, computeType, alg, (size* | buffer)
     "aclsparseSpMMGetBufferSize": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, POINTER(c_size_t)],
     "aclsparseSpMMPreprocess": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P],

@@ -57,6 +57,10 @@ struct ActivePlan {
     int64_t nnz = 0;
     int64_t n = 0;         // SpMM only: dense column count the partial-sum area was sized for
     int32_t segments = 0;  // SpMM only: long-row segments found by the analysis
+    int32_t blockUnits = 0;  // SpMM only: units of the column-block path for the long rows (0 = summed by segments)
+    int32_t longRows = 0;   // SpMM only: rows listed as long
+    const void *colInd = nullptr;  // SpMM with column blocks: the cut table was made from these column indices
+    int32_t valueType = -1;        // ... and for B rows of this element type
     int32_t spmvInfo[B200SP_SPMV_PLAN_INFO_INTS] = {};  // SpMV only: plan_info written by b200sp_spmv_analyze
     uint64_t generation = 0;  // BufferGeneration(buffer) when the analysis was written
 };

@@ -46,9 +46,22 @@ aclsparseStatus_t ValidateSpmm(aclsparseOperation_t opA, aclsparseOperation_t op
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
-aclsparseStatus_t Analyse(const aclsparseSpMatDescr *A, int64_t n, void *buffer, cudaStream_t stream,
-                          int32_t *segments)
+struct Analysis {
+    int32_t segments = 0, blockUnits = 0, longRows = 0;
+};
+
+size_t ElemBytes(aclDataType t)
 {
+    switch (t) {
+        case ACL_FLOAT: case ACL_INT32: return 4;
+        case ACL_FLOAT16: case ACL_BF16: return 2;
+        default: return 1;
+    }
+}
+
+aclsparseStatus_t Analyse(const aclsparseSpMatDescr *A, int64_t n, void *buffer, cudaStream_t stream, Analysis *out)
+{
+    int32_t *segments = &out->segments;
     const size_t bytes = b200sp_spmm_plan_bytes(A->rows, A->nnz, n);
     // Whatever plan this buffer held is overwritten now; an active plan that is not re-recorded below goes stale.
     (void)b200sp::NoteBufferWrite(buffer);
@@ -58,13 +71,24 @@ aclsparseStatus_t Analyse(const aclsparseSpMatDescr *A, int64_t n, void *buffer,
         B200SP_LOGE("aclsparseSpMM: analysis failed (cuda error %d)", rc);
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
+    if (*segments > 0 && A->indices != nullptr) {  // long rows: by column blocks of B where that pays
+        const int rb = b200sp_spmm_analyze_blocks(static_cast<const int32_t *>(A->offsets),
+                                                  static_cast<const int32_t *>(A->indices), A->rows, A->cols, A->nnz,
+                                                  n, n * (int64_t)ElemBytes(A->valueType), buffer, bytes,
+                                                  &out->blockUnits, &out->longRows, stream);
+        if (rb != 0) {
+            B200SP_LOGE("aclsparseSpMM: column-block analysis failed (cuda error %d)", rb);
+            return ACL_SPARSE_STATUS_EXECUTION_FAILED;
+        }
+    }
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 
 bool PlanMatches(const ActivePlan &p, const void *buffer, const aclsparseSpMatDescr *A, int64_t n)
 {
     return p.kind == PlanKind::kSpmm && p.buffer == buffer && p.rowPtr == A->offsets && p.rows == A->rows &&
-           p.nnz == A->nnz && p.n == n && p.generation == b200sp::BufferGeneration(buffer);
+           p.nnz == A->nnz && p.n == n && p.generation == b200sp::BufferGeneration(buffer) &&
+           (p.blockUnits == 0 || (p.colInd == A->indices && p.valueType == (int32_t)A->valueType));
 }
 
 }  // namespace
@@ -99,9 +123,9 @@ aclsparseStatus_t aclsparseSpMMPreprocess(aclsparseHandle_t handle, aclsparseOpe
     if (st != ACL_SPARSE_STATUS_SUCCESS) return st;
     if (buffer == nullptr) return ACL_SPARSE_STATUS_INSUFFICIENT_RESOURCES;
     if (matA->offsets == nullptr) return ACL_SPARSE_STATUS_INVALID_VALUE;
-    int32_t segments = 0;
+    Analysis found;
     const aclsparseStatus_t an =
-        Analyse(matA, matC->cols, buffer, handle != nullptr ? handle->stream : nullptr, &segments);
+        Analyse(matA, matC->cols, buffer, handle != nullptr ? handle->stream : nullptr, &found);
     if (an != ACL_SPARSE_STATUS_SUCCESS) return an;
     // The analysis has just synchronised: the one place on this path where a row-stream product that gave up on a
     // copy (see b200sp_spmm_stream_error) can be reported without adding a synchronisation to a compute call.
@@ -117,7 +141,11 @@ aclsparseStatus_t aclsparseSpMMPreprocess(aclsparseHandle_t handle, aclsparseOpe
     p.rows = matA->rows;
     p.nnz = matA->nnz;
     p.n = matC->cols;
-    p.segments = segments;
+    p.segments = found.segments;
+    p.blockUnits = found.blockUnits;
+    p.longRows = found.longRows;
+    p.colInd = matA->indices;
+    p.valueType = (int32_t)matA->valueType;
     p.generation = b200sp::BufferGeneration(buffer);
     matA->active = p;
     return ACL_SPARSE_STATUS_SUCCESS;
@@ -135,13 +163,15 @@ aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t o
     if (matA->offsets == nullptr || (matA->nnz > 0 && (matA->indices == nullptr || matA->values == nullptr)))
         return ACL_SPARSE_STATUS_INVALID_VALUE;
 
-    int32_t segments = 0;
+    Analysis found;
     if (PlanMatches(matA->active, buffer, matA, matC->cols)) {
-        segments = matA->active.segments;
+        found.segments = matA->active.segments;
+        found.blockUnits = matA->active.blockUnits;
+        found.longRows = matA->active.longRows;
     } else {
         // Not the active buffer: analyse into it now, as the reference rebuilds its tiling
         // in place (spmm_host.cpp:310-321).  This path synchronises the stream once.
-        const aclsparseStatus_t an = Analyse(matA, matC->cols, buffer, handle->stream, &segments);
+        const aclsparseStatus_t an = Analyse(matA, matC->cols, buffer, handle->stream, &found);
         if (an != ACL_SPARSE_STATUS_SUCCESS) return an;
     }
 
@@ -167,12 +197,14 @@ aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t o
     sh.order_b = (matB->order == ACL_SPARSE_ORDER_COL) ? 1 : 0;
     sh.order_c = (matC->order == ACL_SPARSE_ORDER_COL) ? 1 : 0;
     sh.op_b = (opB == ACL_SPARSE_OP_TRANSPOSE) ? 1 : 0;
+    sh.block_units = found.blockUnits;
+    sh.long_rows = found.longRows;
     sh.kahan = (alg == ACL_SPARSE_SPMM_CSR_FP32_HIGH_PRECISION_ALG && matA->valueType == ACL_FLOAT) ? 1 : 0;
 
     const int rc = b200sp_spmm_launch(static_cast<const int32_t *>(matA->offsets),
                                       static_cast<const int32_t *>(matA->indices), matA->values, matB->values,
                                       matC->values, &sh, &sc, b200sp::KernelTypeOf(matA->valueType),
-                                      b200sp::KernelTypeOf(matC->valueType), buffer, segments, handle->stream);
+                                      b200sp::KernelTypeOf(matC->valueType), buffer, found.segments, handle->stream);
     if (rc != 0) {
         B200SP_LOGE("aclsparseSpMM: kernel launch failed (cuda error %d)", rc);
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;

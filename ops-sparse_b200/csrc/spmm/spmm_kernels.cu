@@ -62,9 +62,24 @@ struct LongRow {
     int32_t partBase;  // first partial-row slot (rows of two or more segments only)
 };
 
+// Column blocking of the long rows (see SpmmLongBlockKernel): B is cut into at most kMaxBlocks blocks of
+// consecutive rows, each small enough to stay in L2 while every long row of A sums its entries that fall into it.
+constexpr int kMaxBlocks = 64;
+#ifndef B200SP_SPMM_BLOCK_MB
+#define B200SP_SPMM_BLOCK_MB 32
+#endif
+constexpr long long kBlockBytes = (long long)B200SP_SPMM_BLOCK_MB << 20;  // target size of one block of B rows
+constexpr long long kBlockMinB = 96ll << 20;      // a B smaller than this is left to L2 as a whole
+constexpr int kBlockMinRowBytes = 512;            // B rows narrower than a warp of 16-byte pieces keep the segment CTAs
+#ifndef B200SP_SPMM_UNIT_NNZ
+#define B200SP_SPMM_UNIT_NNZ 256
+#endif
+constexpr int kUnitNnz = B200SP_SPMM_UNIT_NNZ;   // a (row, block) piece longer than this is cut into several units
+
 struct PlanLayout {
-    int64_t capLong, capSegs;
-    size_t offCounts, offLong, offSegs, offCounters, offPartials, total;
+    int64_t capLong, capSegs, capBlockSlots;
+    size_t offCounts, offLong, offSegs, offCounters, offPartials;
+    size_t offCuts, offRowSlots, offBlockCounters, offBlockMeta, offUnits, offBlockPartials, total;
 };
 
 inline PlanLayout LayoutFor(int64_t rows, int64_t nnz, int64_t n)
@@ -80,7 +95,18 @@ inline PlanLayout LayoutFor(int64_t rows, int64_t nnz, int64_t n)
     L.offPartials = AlignUp(L.offCounters + sizeof(int32_t) * (size_t)L.capLong, 256);
     // Only rows of two or more segments store partial rows; those have > kSegNnz entries.
     const int64_t capPartialSegs = 2 * (nnz / kSegNnz) + 1;
-    L.total = AlignUp(L.offPartials + sizeof(float) * (size_t)capPartialSegs * (size_t)n, 256);
+    L.offCuts = AlignUp(L.offPartials + sizeof(float) * (size_t)capPartialSegs * (size_t)n, 256);
+    // Column blocks: a cut table and a {first slot, slots} pair per long row, the unit table and one partial row
+    // per unit, up to a budget of one unit per 128 non-zeros (rows of C at least 128 wide only: narrower ones
+    // never take that path).
+    L.capBlockSlots = n >= 128 ? nnz / 128 + kMaxBlocks : 0;
+    const bool on = L.capBlockSlots > 0;
+    L.offRowSlots = AlignUp(L.offCuts + (on ? sizeof(int32_t) * (size_t)L.capLong * (kMaxBlocks + 1) : 0), 256);
+    L.offBlockCounters = AlignUp(L.offRowSlots + (on ? sizeof(int2) * (size_t)L.capLong : 0), 256);
+    L.offBlockMeta = AlignUp(L.offBlockCounters + (on ? sizeof(int32_t) * (size_t)L.capLong : 0), 256);
+    L.offUnits = AlignUp(L.offBlockMeta + (on ? sizeof(int32_t) * 3 * kMaxBlocks : 0), 256);
+    L.offBlockPartials = AlignUp(L.offUnits + (on ? sizeof(int4) * (size_t)L.capBlockSlots : 0), 256);
+    L.total = AlignUp(L.offBlockPartials + sizeof(float) * (size_t)L.capBlockSlots * (size_t)n, 256);
     return L;
 }
 
@@ -197,6 +223,135 @@ __global__ void SpmmFindLongRowsKernel(const int32_t *__restrict__ rowPtr, int r
         longRows[li] = {(int32_t)r, sb, nseg, pb};
         counters[li] = 0;
         for (int s = 0; s < nseg; ++s) segs[sb + s] = {(int32_t)r, s, li, 0};
+    }
+}
+
+// A warp per long row: checks that its columns ascend, finds where it crosses the boundaries of the column
+// blocks (cut[b] = first entry whose column is >= b * blockCols; cut[blocks] = the row's end) and counts the
+// units (pieces of at most kUnitNnz entries inside one block) of the row and of every block.
+__global__ void __launch_bounds__(256) SpmmCutBlocksKernel(const int32_t *__restrict__ rowPtr,
+                                                           const int32_t *__restrict__ colInd,
+                                                           const LongRow *__restrict__ longRows, int nLong,
+                                                           long long blockCols, int blocks, int32_t *__restrict__ cuts,
+                                                           int2 *__restrict__ rowSlots, int32_t *__restrict__ counters,
+                                                           int32_t *__restrict__ blockUnits, int32_t *unsorted)
+{
+    const int lane = threadIdx.x & 31;
+    const int li = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (li >= nLong) return;
+    const int row = longRows[li].row;
+    const int s = rowPtr[row], e = rowPtr[row + 1];
+    bool bad = false;
+    for (int p = s + lane; p + 1 < e; p += 32) bad |= colInd[p] > colInd[p + 1];
+    if (__any_sync(0xffffffffu, bad)) {
+        if (lane == 0) atomicExch(unsorted, 1);
+    }
+    int32_t *cut = cuts + (long long)li * (kMaxBlocks + 1);
+    for (int b = lane; b <= blocks; b += 32) {
+        int lo = s, hi = e;
+        if (b == blocks) lo = e;
+        const long long target = (long long)b * blockCols;
+        while (lo < hi) {
+            const int mid = lo + ((hi - lo) >> 1);
+            if ((long long)colInd[mid] < target) lo = mid + 1;
+            else hi = mid;
+        }
+        cut[b] = lo;
+    }
+    __syncwarp();
+    int units = 0;
+    for (int b = lane; b < blocks; b += 32) {
+        const int len = cut[b + 1] - cut[b];
+        const int u = len > 0 ? (len + kUnitNnz - 1) / kUnitNnz : 0;  // garbage-in (unsorted) can make len negative
+        if (u > 0) atomicAdd(blockUnits + b, u);
+        units += u;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) units += __shfl_xor_sync(0xffffffffu, units, off);
+    if (lane == 0) {
+        rowSlots[li] = make_int2(0, units);
+        counters[li] = 0;
+    }
+}
+
+// One CTA: first slot of every long row (exclusive scan of the rows' unit counts, in list order) and first unit
+// of every block; the total goes to *total.
+__global__ void __launch_bounds__(1024) SpmmBlockScanKernel(int2 *__restrict__ rowSlots, int nLong,
+                                                            int32_t *__restrict__ blockMeta, int blocks, int32_t *total)
+{
+    __shared__ int sWarp[32];
+    __shared__ int sCarry;
+    if (threadIdx.x == 0) sCarry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < nLong; base += 1024) {
+        const int i = base + threadIdx.x;
+        const int n = i < nLong ? rowSlots[i].y : 0;
+        int incl = n;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += t;
+        }
+        if (lane == 31) sWarp[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = sWarp[lane];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, w, off);
+                if (lane >= off) w += t;
+            }
+            sWarp[lane] = w;  // inclusive over warps
+        }
+        __syncthreads();
+        const int before = sCarry + (warp > 0 ? sWarp[warp - 1] : 0) + incl - n;
+        if (i < nLong) rowSlots[i].x = before;
+        __syncthreads();
+        if (threadIdx.x == 1023) sCarry = before + n;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int b = 0; b < blocks; ++b) {  // blockMeta: [0..64) units of the block, [64..128) first unit, [128..192) filled
+            blockMeta[kMaxBlocks + b] = run;
+            blockMeta[2 * kMaxBlocks + b] = 0;
+            run += blockMeta[b];
+        }
+        *total = sCarry;
+    }
+}
+
+struct BlockUnit {
+    int32_t start, end;  // entries of the row inside one column block
+    int32_t longIdx;
+    int32_t slot;        // partial row this unit writes
+};
+
+// A warp per long row: writes the row's units into the table, block by block (the table is ordered by block; the
+// order inside a block is whatever the atomics give, the slot of a unit is fixed by its place in the row).
+__global__ void __launch_bounds__(256) SpmmFillUnitsKernel(const int32_t *__restrict__ cuts, const int2 *__restrict__ rowSlots,
+                                                           int nLong, int blocks, int32_t *__restrict__ blockMeta,
+                                                           BlockUnit *__restrict__ units, int capUnits)
+{
+    const int lane = threadIdx.x & 31;
+    const int li = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (li >= nLong) return;
+    const int32_t *cut = cuts + (long long)li * (kMaxBlocks + 1);
+    int slot = rowSlots[li].x;
+    for (int b = 0; b < blocks; ++b) {
+        const int s = cut[b], e = cut[b + 1];
+        const int n = e > s ? (e - s + kUnitNnz - 1) / kUnitNnz : 0;
+        if (n == 0) continue;
+        int pos = 0;
+        if (lane == 0) pos = blockMeta[kMaxBlocks + b] + atomicAdd(blockMeta + 2 * kMaxBlocks + b, n);
+        pos = __shfl_sync(0xffffffffu, pos, 0);
+        for (int i = lane; i < n; i += 32) {
+            const int us = s + i * kUnitNnz;
+            if (pos + i < capUnits)
+                units[pos + i] = {us, us + kUnitNnz < e ? us + kUnitNnz : e, li, slot + i};
+        }
+        slot += n;
     }
 }
 
@@ -486,6 +641,168 @@ __global__ void __launch_bounds__(kThreads) SpmmFastKernel(const FastArgs<ValT, 
     }
 }
 
+// ---------------------------------------------------------------- long rows by column blocks
+
+// When B is much larger than L2, a long row of A gathers every one of its B rows from DRAM.  Rows of more than
+// kLongRow entries are few and hold a large share of the non-zeros (a graph's hubs); with ascending columns the
+// entries of such a row that fall into one block of consecutive B rows are contiguous in col_ind.  So B is cut
+// into blocks of about kBlockBytes and the grid walks the pieces (row, block) block by block: while one block
+// is being worked on, every long row gathers from the same few megabytes, which the first touch brings into L2
+// and the evict-last policy of the B loads keeps there.  Pieces are cut into units of at most kUnitNnz entries so
+// that all units take about the same time and the grid stays inside a window of one or two blocks.  A warp sums
+// one unit in CSR order into one partial row; the warp that completes a row adds its partial rows in column
+// order (fixed order: the same bits every run) and applies the epilogue.
+struct BlockArgs {
+    int nUnits;
+    const BlockUnit *units;   // ordered by column block
+    const int2 *rowSlots;     // [long row] {first partial slot, slots}
+    int32_t *counters;        // [long row] arrivals
+    float *partials;          // [slot][n]
+};
+
+// Packed fp32 arithmetic of sm_100: one instruction, two fused multiply-adds.  The long rows are not bound to the
+// golden's separate multiply and add (their sums are regrouped by block anyway), and this kernel, fed from L2,
+// is limited by instruction issue rather than by DRAM.
+__device__ __forceinline__ void Fma2(float2 &acc, float x, float y, float v)
+{
+    unsigned long long a, bq, c;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(x), "f"(y));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(bq) : "f"(v));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(acc.x), "f"(acc.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(a), "l"(bq));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(acc.x), "=f"(acc.y) : "l"(c));
+}
+
+// acc[0 .. E/2) += v * (the E values of 16 bytes of a B row)
+template <typename ValT> struct FusedRow;
+template <> struct FusedRow<float> {
+    static __device__ __forceinline__ void Add(const uint4 &q, float v, float2 (&acc)[2])
+    {
+        Fma2(acc[0], __uint_as_float(q.x), __uint_as_float(q.y), v);
+        Fma2(acc[1], __uint_as_float(q.z), __uint_as_float(q.w), v);
+    }
+};
+template <> struct FusedRow<__nv_bfloat16> {
+    static __device__ __forceinline__ void Add(const uint4 &q, float v, float2 (&acc)[4])
+    {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            Fma2(acc[i], __uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u), v);
+    }
+};
+template <> struct FusedRow<__half> {
+    static __device__ __forceinline__ void Add(const uint4 &q, float v, float2 (&acc)[4])
+    {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&q);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            Fma2(acc[i], f.x, f.y, v);
+        }
+    }
+};
+
+// Measured on the 2 M x 2 M graph matrix with 512-byte rows of B (2,767 long rows, 14.0 M entries), this kernel
+// alone, microseconds: the segment CTAs it replaces 1067 (DRAM-bound: every B row fetched from DRAM);
+// blocks of 16 / 24 / 32 / 48 / 64 MB 848 / 729 / 727 / 715 / 725; units of 128 / 256 / 512 entries
+// 851 / 727 / 813; 2 / 4 / 8 / 16 rows in flight per lane 879 / 727 / 752 / 857; a fixed grid of 4 CTAs per SM
+// walking the units with a stride 1739 (its warps drift apart and the window of blocks in use outgrows L2).
+// At 714 us: 1.9 GB of DRAM traffic instead of 7.2, issue slots 54 % busy (28 warp instructions per B row).
+#ifndef B200SP_SPMM_BLOCK_BATCH
+#define B200SP_SPMM_BLOCK_BATCH 4   // B rows a lane has in flight
+#endif
+#ifndef B200SP_SPMM_BLOCK_CTAS
+#define B200SP_SPMM_BLOCK_CTAS 0    // > 0: a fixed grid of that many CTAs per SM walks the units; 0: a CTA per 4 units
+#endif
+
+template <typename ValT, typename OutT>
+__global__ void __launch_bounds__(kThreads) SpmmLongBlockKernel(const FastArgs<ValT, OutT> a, const BlockArgs b)
+{
+    constexpr int E = Pack<ValT>::kElems;
+    constexpr int kTileCols = 32 * E;
+    constexpr int kBatch = B200SP_SPMM_BLOCK_BATCH;
+    const int lane = threadIdx.x & 31;
+    const long long warpsTotal = (long long)gridDim.x * kWarps;
+    for (long long unit = (long long)blockIdx.x * kWarps + (threadIdx.x >> 5); unit < b.nUnits; unit += warpsTotal) {
+        const int4 raw = __ldg(reinterpret_cast<const int4 *>(b.units) + unit);
+        const int s = raw.x, e = raw.y, li = raw.z, slot = raw.w;
+        float *partial = b.partials + (long long)slot * a.n;
+        for (int col0 = 0; col0 < a.n; col0 += kTileCols) {
+            const int col = col0 + lane * E;
+            const bool colLive = col < a.n;
+            const ValT *Bs = a.B + (colLive ? col : 0);
+            float2 acc[E / 2];
+#pragma unroll
+            for (int i = 0; i < E / 2; ++i) acc[i] = make_float2(0.0f, 0.0f);
+            for (int p0 = s; p0 < e; p0 += 32) {
+                const int cnt = e - p0 < 32 ? e - p0 : 32;
+                int myCol = 0;
+                float myVal = 0.0f;
+                if (lane < cnt) {
+                    myCol = __ldcs(a.colInd + p0 + lane);
+                    myVal = ToF32(__ldcs(a.val + p0 + lane));
+                }
+                int j = 0;
+                for (; j + kBatch <= cnt; j += kBatch) {  // cnt is the same in every lane
+                    uint4 q[kBatch];
+                    float v[kBatch];
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) {
+                        const int c = __shfl_sync(0xffffffffu, myCol, j + u);
+                        v[u] = __shfl_sync(0xffffffffu, myVal, j + u);
+                        q[u] = LoadB16(Bs + (long long)c * a.ldb);
+                    }
+#pragma unroll
+                    for (int u = 0; u < kBatch; ++u) FusedRow<ValT>::Add(q[u], v[u], acc);
+                }
+                for (; j < cnt; ++j) {
+                    const int c = __shfl_sync(0xffffffffu, myCol, j);
+                    const float v = __shfl_sync(0xffffffffu, myVal, j);
+                    const uint4 q = LoadB16(Bs + (long long)c * a.ldb);
+                    FusedRow<ValT>::Add(q, v, acc);
+                }
+            }
+            if (colLive) {
+#pragma unroll
+                for (int i = 0; i < E / 2; i += 2)
+                    __stcg(reinterpret_cast<float4 *>(partial + col + 2 * i),
+                           make_float4(acc[i].x, acc[i].y, acc[i + 1].x, acc[i + 1].y));
+            }
+        }
+        // Arrival: the unit that comes last adds the row's partial rows in slot (= column) order.
+        const int2 rs = __ldg(b.rowSlots + li);
+        __threadfence();
+        int last = 0;
+        if (lane == 0) {
+            const int old = atomicAdd(b.counters + li, 1);
+            last = old == rs.y - 1;
+            if (last) b.counters[li] = 0;  // ready for the next launch
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) continue;
+        __threadfence();
+        const float alpha = a.sc.Alpha();
+        const float beta = a.sc.Beta();
+        const int row = a.longRows[li].row;
+        const float *first = b.partials + (long long)rs.x * a.n;
+        for (int col = lane * E; col < a.n; col += kTileCols) {
+            float tot[E];
+#pragma unroll
+            for (int i = 0; i < E; ++i) tot[i] = 0.0f;
+#pragma unroll 4
+            for (int sl = 0; sl < rs.y; ++sl) {
+#pragma unroll
+                for (int i = 0; i < E; i += 4) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(first + (long long)sl * a.n + col + i));
+                    tot[i] += v.x; tot[i + 1] += v.y; tot[i + 2] += v.z; tot[i + 3] += v.w;
+                }
+            }
+            StoreRowSlice<OutT, E>(a.C + (long long)row * a.ldc + col, tot, alpha, beta);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- row-stream path
 
 // For B rows of 512 or 1024 bytes.  A warp owns 32 consecutive rows of A and walks their
@@ -555,12 +872,28 @@ __device__ __forceinline__ bool MbarWait(uint64_t *bar, uint32_t parity, long lo
     return true;
 }
 // One row: global -> shared through the copy engine; both addresses 16-byte aligned, bytes a multiple of 16.
+// B200SP_SPMM_STREAM_B_POLICY 1: the copies carry an L2 evict-first policy, so that the rows this kernel streams
+// through L2 once do not displace the block of B rows that SpmmLongBlockKernel, running beside it, keeps there.
+// Measured: the row-stream kernel alone slows from 1.90 to 2.01 ms with it and the pair gains nothing; off.
+#ifndef B200SP_SPMM_STREAM_B_POLICY
+#define B200SP_SPMM_STREAM_B_POLICY 0
+#endif
 __device__ __forceinline__ void BulkLoadRow(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
 {
+#if B200SP_SPMM_STREAM_B_POLICY == 1
+    uint64_t pol;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            SmemAddr(dst)),
+        "l"(src), "r"(bytes), "r"(SmemAddr(bar)), "l"(pol)
+        : "memory");
+#else
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                      SmemAddr(dst)),
                  "l"(src), "r"(bytes), "r"(SmemAddr(bar))
                  : "memory");
+#endif
 }
 
 template <int kBytes> struct LaneWords {  // kBytes of shared memory as 32-bit words
@@ -964,7 +1297,6 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
         a.ldb = sh->ldb;
         a.ldc = sh->ldc;
         a.sc = MakeF(s);
-        a.nsegs = segments;
         a.longRows = reinterpret_cast<const LongRow *>(p + L.offLong);
         a.segs = reinterpret_cast<const SegEntry *>(p + L.offSegs);
         a.counters = reinterpret_cast<int32_t *>(p + L.offCounters);
@@ -976,6 +1308,20 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
         // and SpmmFastKernel is launched for its segment CTAs only.
         const long long rowBytes = sh->n * (long long)sizeof(ValT);
         const bool stream_ = !sh->kahan && (rowBytes == 512 || rowBytes == 1024) && sh->m > 0 && B200SP_SPMM_USE_STREAM;
+        // Long rows by column blocks of B (found applicable by b200sp_spmm_analyze_blocks) instead of by segments.
+        const bool byBlocks = sh->block_units > 0 && sh->long_rows > 0 && !sh->kahan && rowBytes >= kBlockMinRowBytes &&
+                              sh->block_units <= L.capBlockSlots;
+        if (byBlocks) segments = 0;
+        a.nsegs = segments;
+        BlockArgs ba{};
+        if (byBlocks) {
+            ba.nUnits = sh->block_units;
+            ba.units = reinterpret_cast<const BlockUnit *>(p + L.offUnits);
+            ba.rowSlots = reinterpret_cast<const int2 *>(p + L.offRowSlots);
+            ba.counters = reinterpret_cast<int32_t *>(p + L.offBlockCounters);
+            ba.partials = reinterpret_cast<float *>(p + L.offBlockPartials);
+        }
+        const long long blockUnits = byBlocks ? (long long)ba.nUnits : 0;
         // With both kernels to run, the segment CTAs (the long rows: few CTAs, each with much work) are forked
         // onto the side stream first and the row-stream kernel shares the SMs with them.
         b200sp::SideLanes *lanes = nullptr;
@@ -983,7 +1329,7 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
 #ifndef B200SP_SPMM_FORK_SEGMENTS
 #define B200SP_SPMM_FORK_SEGMENTS 1
 #endif
-        if (B200SP_SPMM_FORK_SEGMENTS && stream_ && segments > 0) {
+        if (B200SP_SPMM_FORK_SEGMENTS && ((stream_ && segments > 0) || byBlocks)) {
             lanes = b200sp::GetSideLanes();
             if (lanes != nullptr) {
                 if (cudaEventRecord(lanes->fork, stream) != cudaSuccess ||
@@ -1007,10 +1353,20 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
                 default: launch.template operator()<32>(); break;
             }
         };
+        auto launchBlocks = [&](cudaStream_t st) {
+            const long long want = (blockUnits + kWarps - 1) / kWarps;
+            const long long fixed = B200SP_SPMM_BLOCK_CTAS > 0 ? (long long)b200sp_sm_count() * B200SP_SPMM_BLOCK_CTAS : want;
+            SpmmLongBlockKernel<ValT, OutT><<<(unsigned)(want < fixed ? want : fixed), kThreads, 0, st>>>(a, ba);
+            b200sp_note_launches(1);
+        };
         if (lanes != nullptr) {
-            launchFast((unsigned)segments, segStream);
+            if (byBlocks) launchBlocks(segStream);
+            else launchFast((unsigned)segments, segStream);
             if (cudaGetLastError() != cudaSuccess || cudaEventRecord(lanes->join[0], segStream) != cudaSuccess)
                 return (int)cudaErrorLaunchFailure;
+        } else if (byBlocks) {
+            launchBlocks(stream);
+            if (cudaGetLastError() != cudaSuccess) return (int)cudaErrorLaunchFailure;
         }
         if (stream_) {
             StreamArgs<ValT, OutT> sa;
@@ -1029,13 +1385,19 @@ int LaunchFloat(const int32_t *rowPtr, const int32_t *colInd, const void *val, c
                                            : LaunchRowStream<ValT, OutT, 1024>(sa, stream);
             if (rc != 0) return rc;
         }
-        if (lanes != nullptr)  // the segment CTAs are already running beside the row-stream kernel: join them
+        // What is left for SpmmFastKernel on the caller's stream: the segment CTAs unless they were forked (or
+        // replaced by the column-block kernel), and the rows of up to kLongRow entries unless the row-stream
+        // kernel took them.
+        const long long blocks = (lanes != nullptr ? 0 : (long long)segments) +
+                                 (stream_ ? 0 : (sh->m + rowsPerBlock - 1) / rowsPerBlock);
+        if (lanes != nullptr && !stream_) a.nsegs = 0;  // the forked launch had them; these CTAs are all row CTAs
+        if (blocks > 0) {
+            launchFast((unsigned)blocks, stream);
+            if (cudaGetLastError() != cudaSuccess) return (int)cudaErrorLaunchFailure;
+        }
+        if (lanes != nullptr)  // the long rows are already running beside: join them
             return (int)cudaStreamWaitEvent(stream, lanes->join[0], 0);
-        const long long blocks =
-            (long long)segments + (stream_ ? 0 : (sh->m + rowsPerBlock - 1) / rowsPerBlock);
-        if (blocks == 0) return 0;
-        launchFast((unsigned)blocks, stream);
-        return (int)cudaGetLastError();
+        return 0;
     }
     GenericShape g{sh->m, sh->n, sh->ldb, sh->ldc, sh->order_b == 0, sh->order_c == 0, sh->op_b, sh->kahan};
     const long long total = sh->m * sh->n;
@@ -1100,6 +1462,54 @@ int b200sp_spmm_analyze(const int32_t *row_ptr, int64_t rows, int64_t nnz, int64
     e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return (int)e;
     *segments = counts[1];
+    return 0;
+}
+
+int b200sp_spmm_analyze_blocks(const int32_t *row_ptr, const int32_t *col_ind, int64_t rows, int64_t cols,
+                               int64_t nnz, int64_t n, int64_t b_row_bytes, void *plan, size_t plan_bytes,
+                               int32_t *block_units, int32_t *long_rows, void *stream)
+{
+    const PlanLayout L = LayoutFor(rows, nnz, n);
+    if (plan == nullptr || block_units == nullptr || long_rows == nullptr || plan_bytes < L.total)
+        return (int)cudaErrorInvalidValue;
+    *block_units = 0;
+    *long_rows = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char *p = static_cast<char *>(plan);
+    // counts: long rows, segments, partial slots of the segments, "a long row's columns do not ascend", units
+    int32_t counts[5] = {0, 0, 0, 0, 0};
+    cudaError_t e = cudaMemcpyAsync(counts, p + L.offCounts, sizeof(counts), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    const int nLong = counts[0];
+    *long_rows = nLong;
+    if (nLong <= 0 || col_ind == nullptr || L.capBlockSlots == 0 || b_row_bytes < kBlockMinRowBytes ||
+        cols * b_row_bytes < kBlockMinB)
+        return 0;
+    long long blocks = (cols * b_row_bytes + kBlockBytes - 1) / kBlockBytes;
+    if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+    if (blocks < 2) return 0;
+    const long long blockCols = (cols + blocks - 1) / blocks;
+    int32_t *countsDev = reinterpret_cast<int32_t *>(p + L.offCounts);
+    int32_t *meta = reinterpret_cast<int32_t *>(p + L.offBlockMeta);
+    int2 *rowSlots = reinterpret_cast<int2 *>(p + L.offRowSlots);
+    int32_t *cuts = reinterpret_cast<int32_t *>(p + L.offCuts);
+    e = cudaMemsetAsync(meta, 0, sizeof(int32_t) * 3 * kMaxBlocks, st);
+    if (e != cudaSuccess) return (int)e;
+    SpmmCutBlocksKernel<<<(unsigned)((nLong + 7) / 8), 256, 0, st>>>(
+        row_ptr, col_ind, reinterpret_cast<const LongRow *>(p + L.offLong), nLong, blockCols, (int)blocks, cuts,
+        rowSlots, reinterpret_cast<int32_t *>(p + L.offBlockCounters), meta, countsDev + 3);
+    SpmmBlockScanKernel<<<1, 1024, 0, st>>>(rowSlots, nLong, meta, (int)blocks, countsDev + 4);
+    SpmmFillUnitsKernel<<<(unsigned)((nLong + 7) / 8), 256, 0, st>>>(
+        cuts, rowSlots, nLong, (int)blocks, meta, reinterpret_cast<BlockUnit *>(p + L.offUnits),
+        (int)(L.capBlockSlots < INT32_MAX ? L.capBlockSlots : INT32_MAX));
+    b200sp_note_launches(3);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(counts, countsDev, sizeof(counts), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    // Unsorted long rows, or more units than the plan has partial rows for: the segments stay in charge.
+    if (counts[3] == 0 && counts[4] > 0 && counts[4] <= L.capBlockSlots) *block_units = counts[4];
     return 0;
 }
 

@@ -240,6 +240,33 @@ class _Sharded:
     def replication_error(self) -> int:
         return self.exchange.error() if self.exchange is not None else 0
 
+    def _compiled_steps(self, alpha, beta, count, spmm: bool) -> bool:
+        """`count` steps (exchange + product) issued by the library's compiled loop (include/b200sp_bench.h)
+        instead of one Python call per launch; only for the peer exchange.  Returns False when not applicable."""
+        import torch
+
+        if self.exchange is None or count <= 0:
+            return False
+        ex, L, api = self.exchange, self.exchange.L, self.api
+        r0, r1 = ex.my_rows()
+        dense = self.Bs if spmm else self.xs
+        descrs = (c_void_p * ex.REPLICAS)(*[d.raw for d in dense[1:]])
+        out = self.C if spmm else self.y
+        ct = api._compute_type(self.A.values, out.values)
+        a_c, b_c = ctypes.c_float(alpha), ctypes.c_float(beta)
+        if ct == api.ACL_INT32:
+            a_c, b_c = ctypes.c_int32(int(alpha)), ctypes.c_int32(int(beta))
+        head = (ex._ex, c_void_p(self.my_slice.data_ptr()), r0 * ex.row_bytes, (r1 - r0) * ex.row_bytes, ex.seq + 1,
+                ex.REPLICAS, (1 << ex.world) - 1, self.handle.raw)
+        tail = (byref(a_c), self.A.raw, descrs, byref(b_c), out.raw, ct, 0, api._ptr(self.buffer), int(count))
+        with torch.cuda.device(ex.device):
+            rc = L.b200spMgRepeatSpMM(*head, 0, 0, *tail) if spmm else L.b200spMgRepeatSpMV(*head, 0, *tail)
+        if rc != 0:
+            raise RuntimeError(f"compiled step loop returned status {rc}")
+        ex.seq += int(count)
+        self._last = 1 + ex.seq % ex.REPLICAS
+        return True
+
 
 class ShardedSpmv(_Sharded):
     """One rank's share of y = alpha * A x + beta * y.
@@ -265,6 +292,12 @@ class ShardedSpmv(_Sharded):
         which = self._replicate(self.x.values) if broadcast else getattr(self, "_last", 0)
         self._last = which
         self.api.spmv(self.handle, self.A, self.xs[which], self.y, alpha, beta, buffer=self.buffer)
+
+    def steps(self, alpha: float, beta: float, count: int) -> None:
+        """`count` steps with the exchange; through the compiled loop where the peer exchange is in use."""
+        if not self._compiled_steps(alpha, beta, count, spmm=False):
+            for _ in range(count):
+                self.step(alpha, beta)
 
     def close(self) -> None:
         if self.exchange is not None:
@@ -292,6 +325,12 @@ class ShardedSpmm(_Sharded):
         which = self._replicate(self.B.values) if broadcast else getattr(self, "_last", 0)
         self._last = which
         self.api.spmm(self.handle, self.A, self.Bs[which], self.C, alpha, beta, buffer=self.buffer)
+
+    def steps(self, alpha: float, beta: float, count: int) -> None:
+        """`count` steps with the exchange; through the compiled loop where the peer exchange is in use."""
+        if not self._compiled_steps(alpha, beta, count, spmm=True):
+            for _ in range(count):
+                self.step(alpha, beta)
 
     def close(self) -> None:
         if self.exchange is not None:

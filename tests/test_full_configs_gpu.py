@@ -132,8 +132,8 @@ def test_c4_spmm_f32_262144_n64(handle, device, oracle, pkg):
 
 
 def test_c5_spmm_bf16_graph_2m_n256(handle, device, oracle, pkg):
-    """512-byte rows of B: SpmmRowStreamKernel for the rows of up to 1024 entries and the segment CTAs of
-    SpmmFastKernel for the longer ones (up to 65536 entries): two launches per product."""
+    """512-byte rows of B: SpmmRowStreamKernel for the rows of up to 1024 entries and, for the longer ones (up to
+    65536 entries, ascending columns, B of 1 GB), SpmmLongBlockKernel: two launches per product."""
     from ops_sparse_b200 import synth
     cfg = synth.config5()
     A = cfg["A"]

@@ -106,6 +106,13 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
             scale = abs(c["alpha"]) * oracle.spmv_abs_rowsum(rp, ci, v, x_host) + np.abs(c["beta"] * c["y"][r0:r1])
             err = np.abs(y.cpu().numpy().astype(np.float64) - gold)
             ok = ok and bool(np.all(err <= 1e-5 * scale + 1e-30))
+        # the compiled loop: three steps with beta = 0 give the product of the last exchange, whatever ran before
+        op.steps(c["alpha"], 0.0, 3)
+        torch.cuda.synchronize()
+        gold = oracle.spmv(rp, ci, v, x_host, c["y"][r0:r1], c["alpha"], 0.0)
+        scale = abs(c["alpha"]) * oracle.spmv_abs_rowsum(rp, ci, v, x_host)
+        err = np.abs(y.cpu().numpy().astype(np.float64) - gold)
+        ok = ok and bool(np.all(err <= 1e-5 * scale + 1e-30)) and op.exchange.seq == 8
         ok = ok and op.replication_error() == 0
         dist.barrier()
         op.close()

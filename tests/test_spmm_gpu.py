@@ -356,6 +356,82 @@ def test_row_stream_wait_that_runs_out(pkg, handle, device, oracle):
     assert bad == 0, worst
 
 
+def _block_case(rng, m, k, long_rows, lo, hi):
+    """A few long rows with ascending columns among short ones."""
+    from ops_sparse_b200 import synth
+    lengths = rng.integers(0, 40, m)
+    lengths[rng.choice(m, long_rows, replace=False)] = rng.integers(lo, hi, long_rows)
+    return synth.csr_from_lengths(rng, lengths, k, synth.uniform)
+
+
+def _analysed_blocks(pkg, dA, n, row_bytes):
+    """What the two kernel-level analysis passes decide for this matrix: (units of the column-block path, long rows)."""
+    L = pkg.lib()
+    c64, P = ctypes.c_int64, ctypes.c_void_p
+    L.b200sp_spmm_plan_bytes.restype = ctypes.c_size_t
+    L.b200sp_spmm_plan_bytes.argtypes = [c64, c64, c64]
+    L.b200sp_spmm_analyze.argtypes = [P, c64, c64, c64, P, ctypes.c_size_t, ctypes.POINTER(ctypes.c_int32), P]
+    L.b200sp_spmm_analyze_blocks.argtypes = [P, P, c64, c64, c64, c64, c64, P, ctypes.c_size_t,
+                                             ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32), P]
+    nbytes = L.b200sp_spmm_plan_bytes(dA.rows, dA.nnz, n)
+    plan = torch.empty(nbytes, dtype=torch.uint8, device=dA.row_ptr.device)
+    seg, blocks, longs = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+    assert L.b200sp_spmm_analyze(dA.row_ptr.data_ptr(), dA.rows, dA.nnz, n, plan.data_ptr(), nbytes,
+                                 ctypes.byref(seg), None) == 0
+    assert L.b200sp_spmm_analyze_blocks(dA.row_ptr.data_ptr(), dA.col_ind.data_ptr(), dA.rows, dA.cols, dA.nnz, n,
+                                        row_bytes, plan.data_ptr(), nbytes, ctypes.byref(blocks), ctypes.byref(longs),
+                                        None) == 0
+    torch.cuda.synchronize()
+    return blocks.value, longs.value
+
+
+@pytest.mark.parametrize("vt,n", [("bf16", 256), ("f32", 128), ("f32", 264)])
+def test_long_rows_by_column_blocks(pkg, handle, device, oracle, vt, n):
+    """B far larger than L2 and rows of more than 1024 entries with ascending columns: the long rows are summed
+    block by block of B (SpmmLongBlockKernel).  The result must satisfy the usual tolerance, be the same bits on
+    every run, and the analysis must have chosen that path; with one long row's columns out of order it must not."""
+    from ops_sparse_b200 import api
+    rng = np.random.default_rng(97)
+    esize = 2 if vt == "bf16" else 4
+    k = (120 << 20) // (n * esize)              # B of about 120 MB
+    m = 1500
+    A = _block_case(rng, m, k, 40, 1025, 9000)
+    tdt = torch.bfloat16 if vt == "bf16" else torch.float32
+    Bq = torch.from_numpy(rng.standard_normal((k, n)).astype(np.float32)).to(tdt)
+    C0 = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32))
+    vq = torch.from_numpy(A.values).to(tdt)
+    dB = api.DnMat.row_major(Bq.to(device))
+    tol = 2e-3 if vt == "bf16" else 1e-5
+
+    def product(col_ind):
+        dA = api.CsrMatrix(torch.from_numpy(A.row_ptr).to(device), torch.from_numpy(col_ind).to(device),
+                           vq.to(device), m, k)
+        outs = []
+        for _ in range(2):
+            dC = api.DnMat.row_major(C0.to(device))
+            buf = api.spmm_preprocess(handle, dA, dB, dC)
+            api.spmm(handle, dA, dB, dC, 0.75, -0.5, buffer=buf)
+            api.spmm(handle, dA, dB, dC, 0.75, 0.0, buffer=buf)   # the arrival counters must have been reset
+            torch.cuda.synchronize()
+            outs.append(dC.values.clone())
+        assert torch.equal(outs[0], outs[1]), "two runs differ"
+        bad, worst = oracle.check_spmm_f32(A.row_ptr, col_ind, vq.to(torch.float32).numpy(),
+                                           Bq.to(torch.float32).numpy(), C0.numpy(), outs[0].cpu().numpy(),
+                                           0.75, 0.0, tol)
+        assert bad == 0, worst
+        return _analysed_blocks(pkg, dA, n, n * esize)
+
+    blocks, longs = product(A.col_ind)
+    assert longs == 40 and blocks >= 2 * 40
+    # one long row with two columns swapped: not ascending any more, the segment CTAs take the long rows
+    ci = A.col_ind.copy()
+    r = int(np.argmax(np.diff(A.row_ptr)))
+    s = A.row_ptr[r]
+    ci[s + 5], ci[s + 700] = ci[s + 700], ci[s + 5]
+    blocks, longs = product(ci)
+    assert longs == 40 and blocks == 0
+
+
 def test_no_wait_ran_out_in_the_row_stream_kernel(pkg, device):
     """The row-stream kernel bounds its waits on the copy engine and raises a flag when one runs out;
     after everything above it must still be clear.  (Runs last in this file.)"""
