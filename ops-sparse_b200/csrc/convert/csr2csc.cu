@@ -10,8 +10,8 @@
 //   3. every entry is dropped into SOME free slot of its column (an atomic cursor per column) as a 64-bit key:
 //      entry index in the high word, row in the low word;
 //   4. every column segment is sorted by that key (segsort.cuh): ascending entry index IS the golden's order,
-//      whatever order the atomics produced;
-//   5. the keys are split again: row index from the low word, value fetched through the high word.
+//      whatever order the atomics produced; while a sorted segment is stored, its keys are split again: row index
+//      from the low word, value fetched through the high word.
 // A CSC copy of A gives y = A^T x without atomics: aclsparseSpMV (non-transposed) on the CSC arrays read as CSR.
 #include <climits>
 #include <cstdint>
@@ -164,36 +164,70 @@ __global__ void __launch_bounds__(256) ScanApplyKernel(const int *__restrict__ v
     }
 }
 
-// A warp per row: every entry takes the next free slot of its column and leaves (entry index, row) there.
+// Every entry takes the next free slot of its column and leaves (entry index, row) there.  A warp owns
+// kScatterTile consecutive entries, whatever rows they belong to (a row of 16,384 entries is 16 warps' work, a
+// thousand one-entry rows one warp's): the rows of its first and last entry are found by one search each, every
+// entry's row by a search between the two.
+constexpr int kScatterTile = 1024;
+__device__ __forceinline__ int RowOfEntry(const int *__restrict__ rowPtr, int base, int lo, int hi, int e)
+{
+    while (lo < hi) {  // largest r in [lo, hi] with rowPtr[r] - base <= e
+        const int mid = lo + ((hi - lo + 1) >> 1);
+        if (rowPtr[mid] - base <= e) lo = mid;
+        else hi = mid - 1;
+    }
+    return lo;
+}
 __global__ void __launch_bounds__(256) ScatterKeysKernel(const int *__restrict__ rowPtr, const int *__restrict__ colInd,
-                                                         int m, int base, int *__restrict__ cursor,
+                                                         int m, int nnz, int base, int *__restrict__ cursor,
                                                          unsigned long long *__restrict__ keys)
 {
     const int lane = threadIdx.x & 31;
     const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < m; r += warpsTotal) {
-        const int a = rowPtr[r] - base, b = rowPtr[r + 1] - base;
-        for (int e = a + lane; e < b; e += 32) {
+    const long long tiles = ((long long)nnz + kScatterTile - 1) / kScatterTile;
+    for (long long t = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < tiles; t += warpsTotal) {
+        const int e0 = (int)(t * kScatterTile);
+        const int e1 = e0 + kScatterTile < nnz ? e0 + kScatterTile : nnz;
+        int bound = 0;
+        if (lane < 2) bound = RowOfEntry(rowPtr, base, 0, m - 1, lane == 0 ? e0 : e1 - 1);
+        const int r0 = __shfl_sync(0xffffffffu, bound, 0), r1 = __shfl_sync(0xffffffffu, bound, 1);
+        for (int e = e0 + lane; e < e1; e += 32) {
+            const int r = RowOfEntry(rowPtr, base, r0, r1, e);
             const int slot = atomicAdd(cursor + (colInd[e] - base), 1);
             keys[slot] = ((unsigned long long)(unsigned)e << 32) | (unsigned)r;
         }
     }
 }
 
-// cscRowInd[k] = low word + base; cscVal[k] = csrVal[high word] (kBytes per value, 0 = no values).
+// How the sort reads and writes this operator's arrays: the keys lie in the workspace; a sorted key gives its low
+// word (the row) to cscRowInd and fetches the value of the entry its high word names (kBytes per value, 0 = none).
 template <int kBytes>
-__global__ void GatherKernel(const unsigned long long *__restrict__ keys, int base, const void *__restrict__ csrVal,
-                             int nnz, int *__restrict__ cscRowInd, void *__restrict__ cscVal)
-{
-    for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < nnz; k += (long long)gridDim.x * blockDim.x) {
-        const unsigned long long key = keys[k];
+struct Csr2cscIo {
+    const unsigned long long *keys;
+    int base;
+    const void *csrVal;
+    int *cscRowInd;
+    void *cscVal;
+    using Payload = unsigned;
+    __device__ __forceinline__ unsigned long long Load(int a, int i) const { return keys[a + i]; }
+    __device__ __forceinline__ unsigned Fetch(int, unsigned long long key) const
+    {
         const unsigned p = (unsigned)(key >> 32);
-        cscRowInd[k] = (int)(unsigned)(key & 0xffffffffu) + base;
-        if constexpr (kBytes == 1) static_cast<uint8_t *>(cscVal)[k] = static_cast<const uint8_t *>(csrVal)[p];
-        if constexpr (kBytes == 2) static_cast<uint16_t *>(cscVal)[k] = static_cast<const uint16_t *>(csrVal)[p];
-        if constexpr (kBytes == 4) static_cast<uint32_t *>(cscVal)[k] = static_cast<const uint32_t *>(csrVal)[p];
+        if constexpr (kBytes == 1) return static_cast<const uint8_t *>(csrVal)[p];
+        if constexpr (kBytes == 2) return static_cast<const uint16_t *>(csrVal)[p];
+        if constexpr (kBytes == 4) return static_cast<const uint32_t *>(csrVal)[p];
+        return 0u;
     }
-}
+    __device__ __forceinline__ void Commit(int a, int i, unsigned long long key, unsigned value) const
+    {
+        cscRowInd[a + i] = (int)(unsigned)(key & 0xffffffffu) + base;
+        if constexpr (kBytes == 1) static_cast<uint8_t *>(cscVal)[a + i] = (uint8_t)value;
+        if constexpr (kBytes == 2) static_cast<uint16_t *>(cscVal)[a + i] = (uint16_t)value;
+        if constexpr (kBytes == 4) static_cast<uint32_t *>(cscVal)[a + i] = value;
+    }
+    static __device__ __forceinline__ unsigned Pack(unsigned v) { return v; }
+    static __device__ __forceinline__ unsigned Unpack(unsigned v) { return v; }
+};
 
 unsigned Blocks(long long items)
 {
@@ -261,7 +295,7 @@ aclsparseStatus_t aclsparseCsr2cscEx2(aclsparseHandle_t handle, int m, int n, in
     int *list = reinterpret_cast<int *>(p + L.offList);
     const long long counts = (long long)n + 1;
     const int scanBlocks = (int)((counts + kScanBlock - 1) / kScanBlock);
-    const long long warpRows = ((long long)m + 7) / 8;
+    const long long scatterBlocks = (((long long)nnz + kScatterTile - 1) / kScatterTile + 7) / 8;
     const long long cap = (long long)b200sp_sm_count() * 32;
     cudaError_t e = cudaMemsetAsync(cscColPtr, 0, sizeof(int) * (size_t)counts, stream);
     if (e != cudaSuccess) return ACL_SPARSE_STATUS_EXECUTION_FAILED;
@@ -269,28 +303,25 @@ aclsparseStatus_t aclsparseCsr2cscEx2(aclsparseHandle_t handle, int m, int n, in
     ScanBlockSumsKernel<<<(unsigned)scanBlocks, 256, 0, stream>>>(cscColPtr, counts, sums);
     ScanSumsKernel<<<1, 256, 0, stream>>>(sums, scanBlocks);
     ScanApplyKernel<<<(unsigned)scanBlocks, 256, 0, stream>>>(cscColPtr, counts, sums, base, cscColPtr, cursor);
-    ScatterKeysKernel<<<(unsigned)(warpRows < 1 ? 1 : (warpRows < cap ? warpRows : cap)), 256, 0, stream>>>(
-        csrRowPtr, csrColInd, m, base, cursor, keys);
+    ScatterKeysKernel<<<(unsigned)(scatterBlocks < cap ? scatterBlocks : cap), 256, 0, stream>>>(
+        csrRowPtr, csrColInd, m, nnz, base, cursor, keys);
     b200sp_note_launches(5);
     e = cudaGetLastError();
-    if (e == cudaSuccess) e = b200sp_segsort::Sort(cscColPtr, base, n, keys, scratch, list, stream);
+    if (e == cudaSuccess) {
+        auto sort = [&]<int kBytes>() {
+            return b200sp_segsort::Sort(cscColPtr, base, n, Csr2cscIo<kBytes>{keys, base, csrVal, cscRowInd, cscVal}, keys,
+                                        scratch, list, stream);
+        };
+        switch (numeric ? ValueBytes(valType) : 0) {
+            case 1: e = sort.template operator()<1>(); break;
+            case 2: e = sort.template operator()<2>(); break;
+            case 4: e = sort.template operator()<4>(); break;
+            default: e = sort.template operator()<0>(); break;
+        }
+    }
     if (e != cudaSuccess) {
-        B200SP_LOGE("aclsparseCsr2cscEx2: sort failed (%s)", cudaGetErrorString(e));
+        B200SP_LOGE("aclsparseCsr2cscEx2: scatter or sort failed (%s)", cudaGetErrorString(e));
         (void)cudaGetLastError();
-        return ACL_SPARSE_STATUS_EXECUTION_FAILED;
-    }
-    const int bytes = numeric ? ValueBytes(valType) : 0;
-    const unsigned g = Blocks(nnz);
-    switch (bytes) {
-        case 1: GatherKernel<1><<<g, 256, 0, stream>>>(keys, base, csrVal, nnz, cscRowInd, cscVal); break;
-        case 2: GatherKernel<2><<<g, 256, 0, stream>>>(keys, base, csrVal, nnz, cscRowInd, cscVal); break;
-        case 4: GatherKernel<4><<<g, 256, 0, stream>>>(keys, base, csrVal, nnz, cscRowInd, cscVal); break;
-        default: GatherKernel<0><<<g, 256, 0, stream>>>(keys, base, nullptr, nnz, cscRowInd, nullptr); break;
-    }
-    b200sp_note_launches(1);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        B200SP_LOGE("aclsparseCsr2cscEx2: kernel launch failed (%s)", cudaGetErrorString(e));
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
     return ACL_SPARSE_STATUS_SUCCESS;

@@ -4,11 +4,12 @@
 // (sparse/csrsort/arch35/csrsort_host.cpp:52-74, 146-222; sparse/common/aclsparse_matdescr.cpp:25-108).
 // The sort: every entry becomes a 64-bit key (column in the high word, position inside its row in the low word),
 // which makes keys unique and the ascending order of keys exactly the stable order the golden defines
-// (test/csrsort/arch35/csrsort_golden.h:38-70); the rows are then sorted by the segmented sort of segsort.cuh
-// (registers for rows of up to 32 entries, shared memory up to 2048, chunk sort + merge passes beyond), and a last
-// pass splits the keys again: the high word is the sorted column, the low word says which entry of P moves here.
-// Workspace: 8 bytes per entry for the keys, 8 for the merge scratch (whose first half also holds the permuted P
-// until it is copied back) and a list of the rows too long for a warp.
+// (test/csrsort/arch35/csrsort_golden.h:38-70); the rows are sorted by the segmented sort of segsort.cuh
+// (registers for rows of up to 256 entries, shared memory up to 2048, chunk sort + merge passes beyond), which
+// forms the keys while it loads a row and splits them while it stores it: the high word is the sorted column, the
+// low word says which entry of P moves here.  Two launches, no pass of its own over the arrays.
+// Workspace: 8 bytes per entry for the keys and 8 for the merge scratch (both touched only for rows of more than
+// 2048 entries) and a list of the rows too long for a warp.
 #include <cstdint>
 #include <limits>
 #include <new>
@@ -53,43 +54,26 @@ SortLayout SortLayoutFor(int m, int nnz)
     return L;
 }
 
-// A warp per row: keys[e] = column << 32 | (e - row start).
-__global__ void __launch_bounds__(256) CsrsortPackKernel(const int *__restrict__ rowPtr, const int *__restrict__ colInd,
-                                                         int m, int base, unsigned long long *__restrict__ keys)
-{
-    const int lane = threadIdx.x & 31;
-    const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < m; r += warpsTotal) {
-        const int a = rowPtr[r] - base, b = rowPtr[r + 1] - base;
-        for (int e = a + lane; e < b; e += 32)
-            keys[e] = ((unsigned long long)(unsigned)colInd[e] << 32) | (unsigned)(e - a);
+// How the sort reads and writes this operator's arrays: the key of entry i of a row is (column << 32 | i), made on
+// the fly from csrColInd; a sorted key puts its high word back into csrColInd and moves P[row start + low word] to
+// its place (read for the whole row before any of it is written: the sort is in place in both arrays).
+struct CsrsortIo {
+    int *colInd;
+    int *P;
+    using Payload = int;
+    __device__ __forceinline__ unsigned long long Load(int a, int i) const
+    {
+        return ((unsigned long long)(unsigned)colInd[a + i] << 32) | (unsigned)i;
     }
-}
-
-// A warp per row: colInd[e] = high word of keys[e]; permuted[e] = P[row start + low word].
-__global__ void __launch_bounds__(256) CsrsortUnpackKernel(const int *__restrict__ rowPtr, int m, int base,
-                                                           const unsigned long long *__restrict__ keys,
-                                                           int *__restrict__ colInd, const int *__restrict__ P,
-                                                           int *__restrict__ permuted)
-{
-    const int lane = threadIdx.x & 31;
-    const long long warpsTotal = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < m; r += warpsTotal) {
-        const int a = rowPtr[r] - base, b = rowPtr[r + 1] - base;
-        for (int e = a + lane; e < b; e += 32) {
-            const unsigned long long k = keys[e];
-            colInd[e] = (int)(unsigned)(k >> 32);
-            permuted[e] = P[a + (int)(unsigned)(k & 0xffffffffu)];
-        }
+    __device__ __forceinline__ int Fetch(int a, unsigned long long key) const { return P[a + (int)(unsigned)(key & 0xffffffffu)]; }
+    __device__ __forceinline__ void Commit(int a, int i, unsigned long long key, int moved) const
+    {
+        colInd[a + i] = (int)(unsigned)(key >> 32);
+        P[a + i] = moved;
     }
-}
-
-unsigned WarpRowBlocks(int m)
-{
-    const long long want = ((long long)m + 7) / 8;
-    const long long cap = (long long)b200sp_sm_count() * 32;
-    return (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
-}
+    static __device__ __forceinline__ unsigned Pack(int v) { return (unsigned)v; }
+    static __device__ __forceinline__ int Unpack(unsigned v) { return (int)v; }
+};
 
 }  // namespace
 
@@ -154,19 +138,7 @@ aclsparseStatus_t aclsparseXcsrsort(aclsparseHandle_t handle, int m, int n, int 
     auto *scratch = reinterpret_cast<unsigned long long *>(w + L.offScratch);
     auto *list = reinterpret_cast<int *>(w + L.offList);
     const int b = base == ACL_SPARSE_INDEX_BASE_ONE ? 1 : 0;
-    CsrsortPackKernel<<<WarpRowBlocks(m), 256, 0, stream>>>(csrRowPtr, csrColInd, m, b, keys);
-    b200sp_note_launches(1);
-    cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = b200sp_segsort::Sort(csrRowPtr, b, m, keys, scratch, list, stream);
-    if (e == cudaSuccess) {
-        // the merge scratch is free again: its first half takes the permuted P until it is copied over P
-        int *permuted = reinterpret_cast<int *>(scratch);
-        CsrsortUnpackKernel<<<WarpRowBlocks(m), 256, 0, stream>>>(csrRowPtr, m, b, keys, csrColInd, P, permuted);
-        b200sp_note_launches(1);
-        e = cudaGetLastError();
-        if (e == cudaSuccess)
-            e = cudaMemcpyAsync(P, permuted, sizeof(int) * (size_t)nnz, cudaMemcpyDeviceToDevice, stream);
-    }
+    const cudaError_t e = b200sp_segsort::Sort(csrRowPtr, b, m, CsrsortIo{csrColInd, P}, keys, scratch, list, stream);
     if (e != cudaSuccess) {
         B200SP_LOGE("aclsparseXcsrsort: sort failed (%s)", cudaGetErrorString(e));
         (void)cudaGetLastError();
