@@ -94,6 +94,7 @@ __device__ __forceinline__ float Dot16(const uint4 &x, const uint4 &y, float acc
 // aligned: 128-bit loads.  The first 16-byte piece of the X row of every lane stays in registers while
 // consecutive entries of C share their row (rows of up to 32 pieces -- 128 fp32 or 256 fp16 -- are then
 // read once per row and chunk).
+constexpr int kSddmmBatch = 4;  // entries of C a warp works on at once
 template <typename T>
 __global__ void __launch_bounds__(256) SddmmVecKernel(const int32_t *__restrict__ rowPtr, const int32_t *__restrict__ colInd,
                                                       T *__restrict__ cVal, const T *__restrict__ X,
@@ -111,33 +112,66 @@ __global__ void __launch_bounds__(256) SddmmVecKernel(const int32_t *__restrict_
     for (long long c = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); c < chunks; c += warpsTotal) {
         const long long p0 = c * 32;
         const long long p1 = p0 + 32 < nnz ? p0 + 32 : nnz;
-        int lo = 0, hi = m - 1;
-        while (lo < hi) {
-            const int mid = lo + ((hi - lo + 1) >> 1);
-            if ((long long)__ldg(rowPtr + mid) <= p0) lo = mid;
-            else hi = mid - 1;
+        // The row of the chunk's first entry (largest r with rowPtr[r] <= p0): the 32 lanes probe 32 places
+        // per round, so a million rows take four dependent loads instead of twenty.
+        int lo = 0, hi = m;
+        while (hi - lo > 1) {
+            const int step = (hi - lo + 31) / 32;
+            const long long idx = (long long)lo + (long long)(lane + 1) * step;
+            const bool ok = idx < hi && (long long)__ldg(rowPtr + idx) <= p0;
+            const int k = __popc(__ballot_sync(0xffffffffu, ok));  // offsets ascend: the lanes that pass are a prefix
+            lo += k * step;
+            hi = hi < lo + step ? hi : lo + step;
         }
         int r = lo, cachedRow = -1;
         uint4 x0 = make_uint4(0, 0, 0, 0);
         const int myCol = p0 + lane < p1 ? __ldg(colInd + p0 + lane) : 0;  // the chunk's columns, one per lane
-        for (long long p = p0; p < p1; ++p) {
-            while ((long long)__ldg(rowPtr + r + 1) <= p) ++r;
-            const int j = __shfl_sync(0xffffffffu, myCol, (int)(p - p0));
-            const uint4 *xr = X16 + (long long)r * xRow16;
-            const uint4 *yc = Y16 + (long long)j * yRow16;
-            if (r != cachedRow) {
-                if (lane < pieces) x0 = __ldg(xr + lane);
-                cachedRow = r;
-            }
-            float acc = 0.0f;
-            if (lane < pieces) acc = Dot16(x0, __ldg(yc + lane), acc, T());
-            for (int q = lane + 32; q < pieces; q += 32) acc = Dot16(__ldg(xr + q), __ldg(yc + q), acc, T());
+        // Four entries at a time: their Y rows are requested together, so that a warp has four rows in flight
+        // instead of one (the gather of Y rows from DRAM is what this kernel waits for).
+        for (long long p = p0; p < p1; p += kSddmmBatch) {
+            int rows[kSddmmBatch];
+            uint4 y[kSddmmBatch];
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            if (lane == 0) {
-                float z = a * acc;
-                if (b != 0.0f) z += b * Load<T>(cVal + p);
-                cVal[p] = Store<T>(z);
+            for (int u = 0; u < kSddmmBatch; ++u) {
+                const bool live = p + u < p1;
+                if (live) {
+                    while ((long long)__ldg(rowPtr + r + 1) <= p + u) ++r;
+                }
+                rows[u] = r;
+                const int j = __shfl_sync(0xffffffffu, myCol, (int)(p + u - p0) & 31);
+                y[u] = make_uint4(0, 0, 0, 0);
+                if (live && lane < pieces) y[u] = __ldg(Y16 + (long long)j * yRow16 + lane);
+            }
+            float acc[kSddmmBatch];
+#pragma unroll
+            for (int u = 0; u < kSddmmBatch; ++u) {
+                acc[u] = 0.0f;
+                if (p + u >= p1) continue;
+                const uint4 *xr = X16 + (long long)rows[u] * xRow16;
+                if (rows[u] != cachedRow) {
+                    if (lane < pieces) x0 = __ldg(xr + lane);
+                    cachedRow = rows[u];
+                }
+                if (lane < pieces) acc[u] = Dot16(x0, y[u], acc[u], T());
+                if (pieces > 32) {
+                    const int j = __shfl_sync(0xffffffffu, myCol, (int)(p + u - p0) & 31);
+                    const uint4 *yc = Y16 + (long long)j * yRow16;
+                    for (int q = lane + 32; q < pieces; q += 32) acc[u] = Dot16(__ldg(xr + q), __ldg(yc + q), acc[u], T());
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kSddmmBatch; ++u) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], off);
+            }
+            // every lane holds all sums now: lane u writes entry p + u
+            float mine = 0.0f;
+#pragma unroll
+            for (int u = 0; u < kSddmmBatch; ++u) mine = lane == u ? acc[u] : mine;
+            if (lane < kSddmmBatch && p + lane < p1) {
+                float z = a * mine;
+                if (b != 0.0f) z += b * Load<T>(cVal + p + lane);
+                cVal[p + lane] = Store<T>(z);
             }
         }
     }
