@@ -288,7 +288,7 @@ NCU_TRAFFIC = {
            "source": "profiles/spmv_binned_c2_powerlaw_f32.md"},
     "c3": {"bytes": 352_300_000, "kernels": "SpmvShortRowsKernel", "source": "profiles/spmv_binned_c3_stencil27_f16.md"},
     "c4": {"bytes": 635_600_000, "kernels": "SpmmFastKernel", "source": "profiles/spmm_fast_c4_f32_n64.md"},
-    "c5": {"bytes": 18_340_000_000, "kernels": "SpmmRowStreamKernel + SpmmFastKernel",
+    "c5": {"bytes": 13_460_000_000, "kernels": "SpmmRowStreamKernel + SpmmLongBlockKernel",
            "source": "profiles/spmm_rowstream_c5_bf16_n256.md"},
 }
 # What the counters show to be the busy resource where it is not DRAM.
@@ -301,8 +301,9 @@ BOUND_NOTES = {
     "c4": "B (67 MB) is gathered from L2: 4.3 GB move L2->SM per product and that path delivers 18.1-18.4 TB/s "
           "(62-63 B per clock and SM, measured with a pure row-gather probe), so 236 us is the floor of any "
           "formulation that fetches a B row per non-zero",
-    "c5": "B (1.07 GB) exceeds L2: the row gather is DRAM traffic, about 5.5 x the algorithmic bytes (which count "
-          "B once); against that traffic the product runs at about 6.3 TB/s",
+    "c5": "B (1.07 GB) exceeds L2: the rows of up to 1024 entries gather their B rows from DRAM (11.6 GB per product "
+          "at 6.1 TB/s: the row-stream kernel is at the HBM roofline of its traffic); the longer rows (43 % of the "
+          "non-zeros) gather block by block of B through L2 and are bound by instruction issue and L2 latency",
 }
 
 
@@ -315,13 +316,18 @@ class Env:
     pass
 
 
-def kernels_of(is_spmm: bool, launches_per_step: float, b_row_bytes: int, world: int) -> str:
-    """The kernels one step launches, as the library's routing rules give them."""
+def kernels_of(is_spmm: bool, launches_per_step: float, b_row_bytes: int, world: int, plan=(0, 0, 0, 0)) -> str:
+    """The kernels one step launches, as the library's routing rules give them (`plan`: b200spSpMMPlanInfo)."""
     if is_spmm:
+        if plan[1] > 0:
+            long_rows = " + SpmmLongBlockKernel (rows > 1024 nnz, block by block of B through L2, side stream)"
+        elif plan[0] > 0:
+            long_rows = " + SpmmFastKernel (segment CTAs of rows > 1024 nnz, side stream)"
+        else:
+            long_rows = ""
         if b_row_bytes in (512, 1024):
-            return ("SpmmRowStreamKernel" + (" + SpmmFastKernel (segment CTAs of rows > 1024 nnz, side stream)"
-                                             if launches_per_step > 1 + (world > 1) else ""))
-        return "SpmmFastKernel"
+            return "SpmmRowStreamKernel" + long_rows
+        return "SpmmFastKernel" + (long_rows if plan[1] > 0 else "")
     if launches_per_step >= 2 + (world > 1):
         return "SpmvLongBlockKernel (side stream) + SpmvMediumShortKernel"
     return "SpmvShortRowsKernel | SpmvMediumShortKernel | SpmvAllBinsKernel"
@@ -522,9 +528,12 @@ def measure_config(name: str, args, env, head: bool) -> dict:
         base = cpu_baseline(cfg, oracle, oracle.hardware_threads())
 
     lps = launches / K
-    kernels = kernels_of(is_spmm, lps, n * dense.element_size() if is_spmm else 0, world)
+    plan = (ctypes.c_int32 * 4)()
+    if is_spmm:
+        L.b200spSpMMPlanInfo(op.A.raw, plan)
+    kernels = kernels_of(is_spmm, lps, n * dense.element_size() if is_spmm else 0, world, tuple(plan))
     traffic = NCU_TRAFFIC.get(name) if world == 1 else None
-    if traffic is not None and traffic["kernels"].split(" ")[0] not in kernels:
+    if traffic is not None and any(k not in kernels for k in traffic["kernels"].split(" + ")):
         traffic = None
     res = {
         "metric": metric_name(cfg), "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -691,7 +700,7 @@ def aux_arm(args, synth, oracle):
         alg = 4 * (m + 1) + 16 * nnz  # col_ind and P: read once, written once
         workload = {"workload": "csrsort of the c2 pattern, columns shuffled inside every row", "rows": m, "nnz": nnz,
                     "workspace_bytes": int(size.value)}
-        kernels = "CsrsortPackKernel + SegSortShortKernel + SegSortLongKernel + CsrsortUnpackKernel + D2D copy of P"
+        kernels = "SegSortWarpKernel + SegSortCtaKernel (keys formed and split inside the sort)"
     elif args.op == "csr2csc":
         d_v = to(A.values)
         o_v, o_ri = torch.empty_like(d_v), torch.empty_like(d_ci)
@@ -711,8 +720,8 @@ def aux_arm(args, synth, oracle):
         alg = 4 * (m + 1) + 8 * nnz + 4 * (n + 1) + 8 * nnz
         workload = {"workload": "csr2csc (numeric, fp32) of the c2 matrix", "rows": m, "cols": n, "nnz": nnz,
                     "workspace_bytes": int(size.value)}
-        kernels = ("ColumnHistogramKernel + Scan{BlockSums,Sums,Apply}Kernel + ScatterKeysKernel + SegSort{Short,Long}Kernel"
-                   " + GatherKernel")
+        kernels = ("ColumnHistogramKernel + Scan{BlockSums,Sums,Apply}Kernel + ScatterKeysKernel + "
+                   "SegSort{Warp,Cta}Kernel")
     elif args.op in ("spmvop-alg1", "spmvop-alg2"):
         # the SpMVOp plan API (compensated row sums) on the c2 matrix, Z aliasing Y
         cfg = synth.config2()
@@ -774,7 +783,7 @@ def aux_arm(args, synth, oracle):
                     "gather_bytes": int(nnz) * 2 * k * 2,
                     "note": "the Y row of every entry is its own 512-byte read: the gather (nnz * 1 KB with X) is what "
                             "moves, the algorithmic bytes count X and Y once"}
-        kernels = "SddmmKernel"
+        kernels = "SddmmVecKernel"
     ms = float(np.median(t))
     line = {"op": args.op, "metric": f"{args.op}_ms", "value": ms, "unit": "ms", "higher_is_better": False, "n_gpus": 1,
             "steps": K, "warmup": 3, "per_step_ms": {"min": float(t.min()), "median": ms, "max": float(t.max())},

@@ -27,6 +27,10 @@ aclsparseStatus_t b200spRepeatSpMM(aclsparseHandle_t handle, aclsparseOperation_
                                    aclsparseConstDnMatDescr_t matB, const void *beta, aclsparseDnMatDescr_t matC,
                                    aclDataType computeType, aclsparseSpMMAlg_t alg, void *buffer, int reps);
 
+/* What aclsparseSpMMPreprocess recorded for matA: info = {long-row segments, units of the column-block path
+ * (0 = the long rows are summed by segments), long rows, 1 if a plan is recorded}. */
+aclsparseStatus_t b200spSpMMPlanInfo(aclsparseConstSpMatDescr_t matA, int32_t info[4]);
+
 /* Row-sharded operator on several GPUs: `reps` steps, step i = b200spMgPush of this rank's slice (`slice`,
  * `offset`, `bytes` as for b200spMgPush) with sequence number firstSeq + i into replica (firstSeq + i) % replicas,
  * on the handle's stream, followed by the product against that replica's descriptor

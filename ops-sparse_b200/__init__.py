@@ -103,6 +103,7 @@ _SIGNATURES = {
     "aclsparseSpMV": [P, c_int, P, P, P, P, P, c_int, c_int, P],
     "b200spRepeatSpMV": [P, c_int, P, P, P, P, P, c_int, c_int, P, c_int],
     "b200spRepeatSpMM": [P, c_int, c_int, P, P, P, P, P, c_int, c_int, P, c_int],
+    "b200spSpMMPlanInfo": [P, POINTER(c_int32)],
     # exchange, slice, offset, bytes, firstSeq, replicas, waitMask, then the product's arguments with an array of
     # per-replica dense descriptors, reps
     "b200spMgRepeatSpMV": [P, P, c_size_t, c_size_t, c_uint32, c_int, c_uint32, P, c_int, P, P, P, P, P, c_int, c_int,

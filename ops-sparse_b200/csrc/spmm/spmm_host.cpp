@@ -9,6 +9,7 @@
 // Extension: (bf16, bf16, f32 | bf16, compute f32) is accepted besides the reference's
 // three type combinations (spmm_host.cpp:108-112).
 #include "../common/internal.h"
+#include "b200sp_bench.h"
 
 namespace {
 
@@ -209,6 +210,19 @@ aclsparseStatus_t aclsparseSpMM(aclsparseHandle_t handle, aclsparseOperation_t o
         B200SP_LOGE("aclsparseSpMM: kernel launch failed (cuda error %d)", rc);
         return ACL_SPARSE_STATUS_EXECUTION_FAILED;
     }
+    return ACL_SPARSE_STATUS_SUCCESS;
+}
+
+// What the analysis recorded in matA's active SpMM plan: info = {segments, units of the column-block path, long
+// rows, 1 if a plan is recorded at all}.  For benchmarks and tests that must say which kernels a product runs.
+aclsparseStatus_t b200spSpMMPlanInfo(aclsparseConstSpMatDescr_t matA, int32_t info[4])
+{
+    if (matA == nullptr || info == nullptr) return ACL_SPARSE_STATUS_INVALID_VALUE;
+    const bool on = matA->active.kind == PlanKind::kSpmm;
+    info[0] = on ? matA->active.segments : 0;
+    info[1] = on ? matA->active.blockUnits : 0;
+    info[2] = on ? matA->active.longRows : 0;
+    info[3] = on ? 1 : 0;
     return ACL_SPARSE_STATUS_SUCCESS;
 }
 

@@ -70,7 +70,8 @@ def _run_spmv(cfg, handle, device, oracle, pkg, expect_kind=None, expect_launche
     return info
 
 
-def _run_spmm(cfg, handle, device, oracle, pkg, expect_launches=None):
+def _run_spmm(cfg, handle, device, oracle, pkg, expect_launches=None, expect_blocks=None):
+    import ctypes
     from ops_sparse_b200 import api
     A = cfg["A"]
     vt, ot = TORCH[cfg["val"]], TORCH[cfg["out"]]
@@ -81,6 +82,10 @@ def _run_spmm(cfg, handle, device, oracle, pkg, expect_launches=None):
     dA = api.CsrMatrix(d_rp, d_ci, d_v, A.rows, A.cols)
     dB, dC = api.DnMat.row_major(d_B), api.DnMat.row_major(d_C)
     buf = api.spmm_preprocess(handle, dA, dB, dC)
+    plan = (ctypes.c_int32 * 4)()
+    assert pkg.lib().b200spSpMMPlanInfo(dA.raw, plan) == 0 and plan[3] == 1
+    if expect_blocks is not None:  # long rows by column blocks of B (units > 0) or by segments (units == 0)
+        assert (plan[1] > 0) == expect_blocks, list(plan)
     before = _launches(pkg)
     api.spmm(handle, dA, dB, dC, cfg["alpha"], cfg["beta"], buffer=buf)
     torch.cuda.synchronize()
@@ -128,7 +133,7 @@ def test_c4_spmm_f32_262144_n64(handle, device, oracle, pkg):
     from ops_sparse_b200 import synth
     cfg = synth.config4()
     assert cfg["A"].rows == 262144 and cfg["B"].shape == (262144, 64)
-    _run_spmm(cfg, handle, device, oracle, pkg, expect_launches=1)  # SpmmFastKernel alone
+    _run_spmm(cfg, handle, device, oracle, pkg, expect_launches=1, expect_blocks=False)  # SpmmFastKernel alone
 
 
 def test_c5_spmm_bf16_graph_2m_n256(handle, device, oracle, pkg):
@@ -138,4 +143,4 @@ def test_c5_spmm_bf16_graph_2m_n256(handle, device, oracle, pkg):
     cfg = synth.config5()
     A = cfg["A"]
     assert A.rows == 1 << 21 and cfg["B"].shape == (1 << 21, 256) and int(A.lengths().max()) > 4096
-    _run_spmm(cfg, handle, device, oracle, pkg, expect_launches=2)
+    _run_spmm(cfg, handle, device, oracle, pkg, expect_launches=2, expect_blocks=True)
