@@ -629,8 +629,13 @@ struct LongBlockArgs {
 // column indices ascend.  kPieceLanes lanes share a piece; x comes from shared memory, so the
 // only global traffic is the col_ind / values stream.  The last CTA of a row group to finish
 // adds each row's partial sums in block order (no wait, fixed order) and writes y.
+// Registers are capped at 48 (not at the 64 a 1024-thread CTA could have): while this kernel holds an SM, the
+// CTAs of the medium / short grid get what is left of the register file, and both grids are bound by latency x
+// occupancy.  Timestamps taken inside the kernels on the power-law matrix: these CTAs run 30-43 us, all done 47 us
+// after the first started; the medium rows beside them finish at 68 us instead of 35 alone, the short rows at
+// 91.  Product time with 56 / 46 / 40 registers here: 90.2 / 86.4 / 89.2 us.
 template <typename CompT, typename ValT, typename OutT, bool kVec>
-__global__ void __launch_bounds__(kLongBlockThreads) SpmvLongBlockKernel(const LongBlockArgs<CompT, ValT, OutT> a)
+__global__ void __maxnreg__(48) SpmvLongBlockKernel(const LongBlockArgs<CompT, ValT, OutT> a)
 {
     extern __shared__ __align__(16) unsigned char sRaw[];
     ValT *xs = reinterpret_cast<ValT *>(sRaw);
