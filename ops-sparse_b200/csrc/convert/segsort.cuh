@@ -8,11 +8,11 @@
 //   segments of up to 256 keys   a warp per segment; every lane holds 1, 2, 4 or 8 keys in registers and the
 //                                bitonic network runs over shuffles (partners in other lanes) and register pairs
 //                                (partners in the same lane): no shared memory, no barrier;
-//   up to kSegChunk = 2048 keys  a CTA per segment: its eight warps sort 256 keys each as above, then three
-//                                merge rounds in shared memory (merge path: every thread finds its eight outputs
-//                                by a binary search on a diagonal and merges them sequentially);
-//   longer                       the same CTA sorts the segment chunk by chunk into the key array, then merges the
-//                                sorted runs pairwise between the key array and a scratch array until one is left.
+//   up to kSegChunk = 2048 keys  a CTA per segment: a stable radix sort on the high word, 8 bits per pass, as many
+//                                passes as the segment's largest high word has bytes, between two shared-memory
+//                                buffers (the low word needs no pass: the keys arrive ordered by it, or the high
+//                                words are unique);
+//   longer                       the same passes between the key array and a scratch array in global memory.
 // The callers' own passes are folded into the sort through an `Io` policy: keys are formed while they are loaded
 // (`Load(a, i)`: element i of the segment that starts at a) and split into the callers' outputs while they are
 // stored (`Fetch(a, key)` reads what the stored element needs, for all elements of the segment, before
@@ -126,73 +126,87 @@ static __global__ void __launch_bounds__(256) SegSortWarpKernel(const int *__res
     }
 }
 
-// The first d outputs of the merge of the sorted runs A[0, na) and B[0, nb) take `ai` keys of A: returns ai.
-__device__ __forceinline__ int MergePathSplit(const unsigned long long *A, int na, const unsigned long long *B, int nb, int d)
-{
-    int l = d - nb > 0 ? d - nb : 0, h = d < na ? d : na;
-    while (l < h) {
-        const int m = (l + h) >> 1;
-        if (A[m] < B[d - m - 1]) l = m + 1;  // real keys are unique; sentinels may tie, in any order
-        else h = m;
-    }
-    return l;
-}
+constexpr int kRadixBits = 8;
+constexpr int kBins = 1 << kRadixBits;
+constexpr int kCtaWarps = kSegThreads / 32;
+static_assert(kBins == kSegThreads, "the scan below gives every thread one bin");
 
-// Merges the sorted runs src[lo, mid) and src[mid, hi) into dst[lo, hi); all threads of the CTA call it.
-__device__ __forceinline__ void MergeRuns(const unsigned long long *__restrict__ src, unsigned long long *__restrict__ dst,
-                                          int lo, int mid, int hi)
-{
-    const int na = mid - lo, nb = hi - mid, n = na + nb;
-    const int per = (n + kSegThreads - 1) / kSegThreads;
-    const int d0 = (int)threadIdx.x * per < n ? (int)threadIdx.x * per : n;
-    const int d1 = d0 + per < n ? d0 + per : n;
-    if (d0 >= d1) return;
-    const unsigned long long *A = src + lo, *B = src + mid;
-    int ai = MergePathSplit(A, na, B, nb, d0), bi = d0 - ai;
-    for (int o = d0; o < d1; ++o) {
-        const bool takeA = bi >= nb || (ai < na && A[ai] < B[bi]);
-        dst[lo + o] = takeA ? A[ai++] : B[bi++];
-    }
-}
-
-// Sorts n <= kSegChunk keys by the whole CTA: keys come from load(i), the sorted keys end up in the returned
-// shared-memory buffer (one of s0 / s1), padded with sentinels up to kSegChunk.
-template <class LoadFn>
-__device__ __forceinline__ unsigned long long *ChunkSort(unsigned long long *s0, unsigned long long *s1, int n, LoadFn load)
+// One stable pass of a CTA-wide least-significant-digit radix sort: n keys in their current order load(0 .. n)
+// go to store(position, key), ordered by bits [shift, shift + 8) and, among equal digits, by current order.
+// Every warp owns a contiguous slice of the current order; after a histogram per warp and one scan over
+// (digit, warp), a warp walks its slice 32 keys at a time and ranks equal digits by lane with match.any:
+// no barrier and no counter reset inside the walk.  sHist holds kBins * kCtaWarps counters, sPart kCtaWarps.
+template <class LoadFn, class StoreFn>
+__device__ __forceinline__ void RadixPass(int n, int shift, int *sHist, int *sPart, LoadFn load, StoreFn store)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    {
-        unsigned long long v[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const int i = warp * kWarpMax + r * 32 + lane;
-            v[r] = i < n ? load(i) : kSentinel;
-        }
-        if (warp * kWarpMax < n) WarpSort<8>(v, lane);  // a run of sentinels alone is sorted already
-#pragma unroll
-        for (int r = 0; r < 8; ++r) s0[warp * kWarpMax + r * 32 + lane] = v[r];
+    const int per = ((n + kCtaWarps - 1) / kCtaWarps + 31) & ~31;
+    const int w0 = warp * per < n ? warp * per : n;
+    const int w1 = w0 + per < n ? w0 + per : n;
+    for (int i = threadIdx.x; i < kBins * kCtaWarps; i += kSegThreads) sHist[i] = 0;
+    __syncthreads();
+    for (int i = w0 + lane; i < w1; i += 32) {
+        const unsigned d = (unsigned)(load(i) >> shift) & (kBins - 1);
+        atomicAdd(&sHist[d * kCtaWarps + warp], 1);
     }
     __syncthreads();
-    unsigned long long *src = s0, *dst = s1;
-    for (int width = kWarpMax; width < kSegChunk && width < n; width <<= 1) {
-        // thread t writes outputs [t * 8, t * 8 + 8): they lie inside one pair of runs
-        const int o0 = (int)threadIdx.x * kPerThread;
-        const int lo = o0 / (2 * width) * (2 * width);
-        const unsigned long long *A = src + lo, *B = src + lo + width;
-        const int d0 = o0 - lo;
-        int ai = MergePathSplit(A, width, B, width, d0), bi = d0 - ai;
+    {  // exclusive scan over (digit, warp): thread t owns digit t
+        int c[kCtaWarps], tot = 0;
 #pragma unroll
-        for (int o = 0; o < kPerThread; ++o) {
-            const bool takeA = bi >= width || (ai < width && A[ai] < B[bi]);
-            dst[o0 + o] = takeA ? A[ai++] : B[bi++];
+        for (int w = 0; w < kCtaWarps; ++w) {
+            c[w] = sHist[threadIdx.x * kCtaWarps + w];
+            tot += c[w];
         }
+        int incl = tot;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += t;
+        }
+        if (lane == 31) sPart[warp] = incl;
         __syncthreads();
-        unsigned long long *t = src;
-        src = dst;
-        dst = t;
+        int before = incl - tot;
+        for (int w = 0; w < warp; ++w) before += sPart[w];
+#pragma unroll
+        for (int w = 0; w < kCtaWarps; ++w) {
+            sHist[threadIdx.x * kCtaWarps + w] = before;
+            before += c[w];
+        }
     }
-    // Runs beyond the last merged width hold sentinels only (width >= n), so src[0, n) is the sorted segment.
-    return src;
+    __syncthreads();
+    for (int i0 = w0; i0 < w1; i0 += 32) {
+        const int i = i0 + lane;
+        const bool live = i < w1;
+        const unsigned long long key = live ? load(i) : 0ull;
+        const unsigned d = live ? ((unsigned)(key >> shift) & (kBins - 1)) : (unsigned)kBins;  // idle lanes: a group apart
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        int pos = 0;
+        if (live) pos = sHist[d * kCtaWarps + warp] + rank;
+        __syncwarp();
+        if (live && rank == 0) sHist[d * kCtaWarps + warp] += __popc(peers);  // the lowest lane of every group
+        __syncwarp();
+        if (live) store(pos, key);
+    }
+    __syncthreads();
+}
+
+// Passes needed for the high words of a segment's keys: the CTA ORs them together and counts the bytes in use.
+template <class LoadFn>
+__device__ __forceinline__ int RadixPasses(int n, int *sWord, LoadFn load)
+{
+    if (threadIdx.x == 0) *sWord = 0;
+    __syncthreads();
+    unsigned seen = 0;
+    for (int i = threadIdx.x; i < n; i += kSegThreads) seen |= (unsigned)(load(i) >> 32);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) seen |= __shfl_xor_sync(0xffffffffu, seen, off);
+    if ((threadIdx.x & 31) == 0 && seen != 0) atomicOr(sWord, (int)seen);
+    __syncthreads();
+    const unsigned all = (unsigned)*sWord;
+    __syncthreads();
+    const int bits = all == 0 ? 1 : 32 - __clz(all);
+    return (bits + kRadixBits - 1) / kRadixBits;
 }
 
 template <class Io>
@@ -204,7 +218,9 @@ static __global__ void __launch_bounds__(kSegThreads) SegSortCtaKernel(const int
 {
     __shared__ unsigned long long s0[kSegChunk];
     __shared__ unsigned long long s1[kSegChunk];
-    __shared__ int sTake;
+    __shared__ int sHist[kBins * kCtaWarps];
+    __shared__ int sPart[kCtaWarps];
+    __shared__ int sTake, sWord;
     const int medium = longList[0], big = longList[1];
     for (;;) {
         __syncthreads();
@@ -215,8 +231,25 @@ static __global__ void __launch_bounds__(kSegThreads) SegSortCtaKernel(const int
         const int seg = li < big ? longList[kListHead + segments - 1 - li] : longList[kListHead + li - big];
         const int a = offsets[seg] - base;
         const int len = offsets[seg + 1] - base - a;
-        if (len <= kSegChunk) {
-            const unsigned long long *sorted = ChunkSort(s0, s1, len, [&](int i) { return io.Load(a, i); });
+        auto fromCaller = [&](int i) { return io.Load(a, i); };
+        const int passes = RadixPasses(len, &sWord, fromCaller);
+        if (len <= kSegChunk) {  // between two shared-memory buffers
+            unsigned long long *src = s1, *dst = s0;
+            for (int p = 0; p < passes; ++p) {
+                const int shift = 32 + kRadixBits * p;
+                unsigned long long *to = dst;
+                if (p == 0) {
+                    RadixPass(len, shift, sHist, sPart, fromCaller, [&](int j, unsigned long long k) { to[j] = k; });
+                } else {
+                    const unsigned long long *from = src;
+                    RadixPass(len, shift, sHist, sPart, [&](int i) { return from[i]; },
+                              [&](int j, unsigned long long k) { to[j] = k; });
+                }
+                unsigned long long *t = src;
+                src = dst;
+                dst = t;
+            }
+            const unsigned long long *sorted = src;
             unsigned long long key[kPerThread];
             typename Io::Payload pay[kPerThread];
 #pragma unroll
@@ -231,41 +264,31 @@ static __global__ void __launch_bounds__(kSegThreads) SegSortCtaKernel(const int
                 const int i = o * kSegThreads + (int)threadIdx.x;
                 if (i < len) io.Commit(a, i, key[o], pay[o]);
             }
-            __syncthreads();
             continue;
         }
-        // Longer than a chunk: sorted chunks go to the key array, then pairwise merges between it and the scratch.
-        for (int c0 = 0; c0 < len; c0 += kSegChunk) {
-            const int n = len - c0 < kSegChunk ? len - c0 : kSegChunk;
-            const unsigned long long *sorted = ChunkSort(s0, s1, n, [&](int i) { return io.Load(a, c0 + i); });
-            for (int i = threadIdx.x; i < n; i += kSegThreads) data[a + c0 + i] = sorted[i];
-            __syncthreads();
-        }
+        // Longer than a chunk: between the scratch array and the key array in global memory (the first pass writes
+        // the scratch array: a caller may keep its unsorted keys in the key array).
         unsigned long long *src = data, *dst = scratch;
-        for (int width = kSegChunk; width < len; width <<= 1) {
-            __threadfence_block();
-            __syncthreads();  // the previous pass (or the chunk sorts) are complete and visible to the whole CTA
-            for (int lo = 0; lo < len; lo += 2 * width) {
-                const int mid = lo + width < len ? lo + width : len;
-                const int hi = lo + 2 * width < len ? lo + 2 * width : len;
-                if (mid < hi) MergeRuns(src, dst, a + lo, a + mid, a + hi);
-                else
-                    for (int i = lo + threadIdx.x; i < hi; i += kSegThreads) dst[a + i] = src[a + i];  // an odd run out
+        for (int p = 0; p < passes; ++p) {
+            const int shift = 32 + kRadixBits * p;
+            unsigned long long *to = dst + a;
+            if (p == 0) {
+                RadixPass(len, shift, sHist, sPart, fromCaller, [&](int j, unsigned long long k) { to[j] = k; });
+            } else {
+                const unsigned long long *from = src + a;
+                RadixPass(len, shift, sHist, sPart, [&](int i) { return from[i]; },
+                          [&](int j, unsigned long long k) { to[j] = k; });
             }
             unsigned long long *t = src;
             src = dst;
             dst = t;
         }
-        __threadfence_block();
-        __syncthreads();
-        // Split the sorted keys into the caller's outputs, a chunk at a time: what Commit needs is fetched for the
-        // whole segment first and parked in the array the sorted keys are NOT in (4 bytes per element).
-        unsigned *park = reinterpret_cast<unsigned *>((src == data ? scratch : data) + a);
+        // Split the sorted keys into the caller's outputs: what Commit needs is fetched for the whole segment
+        // first and parked in the array the sorted keys are NOT in (4 bytes per element).
+        unsigned *park = reinterpret_cast<unsigned *>(dst + a);
         for (int i = threadIdx.x; i < len; i += kSegThreads) park[i] = Io::Pack(io.Fetch(a, src[a + i]));
-        __threadfence_block();
         __syncthreads();
         for (int i = threadIdx.x; i < len; i += kSegThreads) io.Commit(a, i, src[a + i], Io::Unpack(park[i]));
-        __syncthreads();
     }
 }
 
