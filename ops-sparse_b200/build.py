@@ -65,7 +65,7 @@ def _stamp(paths: list[Path], extra: str) -> str:
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile every source for sm_100a and link the shared library.  Returns its path."""
     srcs = [CSRC / s for s in SOURCES]
-    headers = sorted(CSRC.rglob("*.h")) + sorted((ROOT / "include").rglob("*.h"))
+    headers = sorted(CSRC.rglob("*.h")) + sorted(CSRC.rglob("*.cuh")) + sorted((ROOT / "include").rglob("*.h"))
     stamp = _stamp(srcs + headers, " ".join(NVCC_FLAGS))
     stamp_file = LIB_DIR / "build.stamp"
     if not force and LIB_PATH.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:

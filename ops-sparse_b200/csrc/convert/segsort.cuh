@@ -145,16 +145,20 @@ __device__ __forceinline__ void RadixPass(int n, int shift, int *sHist, int *sPa
     const int w1 = w0 + per < n ? w0 + per : n;
     for (int i = threadIdx.x; i < kBins * kCtaWarps; i += kSegThreads) sHist[i] = 0;
     __syncthreads();
-    for (int i = w0 + lane; i < w1; i += 32) {
-        const unsigned d = (unsigned)(load(i) >> shift) & (kBins - 1);
-        atomicAdd(&sHist[d * kCtaWarps + warp], 1);
+    for (int i = w0 + lane; i < w1; i += 4 * 32) {  // four loads in flight per lane
+        unsigned long long k[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) k[u] = i + 32 * u < w1 ? load(i + 32 * u) : 0ull;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i + 32 * u < w1) atomicAdd(&sHist[warp * kBins + ((unsigned)(k[u] >> shift) & (kBins - 1))], 1);
     }
     __syncthreads();
     {  // exclusive scan over (digit, warp): thread t owns digit t
         int c[kCtaWarps], tot = 0;
 #pragma unroll
         for (int w = 0; w < kCtaWarps; ++w) {
-            c[w] = sHist[threadIdx.x * kCtaWarps + w];
+            c[w] = sHist[w * kBins + threadIdx.x];
             tot += c[w];
         }
         int incl = tot;
@@ -169,22 +173,24 @@ __device__ __forceinline__ void RadixPass(int n, int shift, int *sHist, int *sPa
         for (int w = 0; w < warp; ++w) before += sPart[w];
 #pragma unroll
         for (int w = 0; w < kCtaWarps; ++w) {
-            sHist[threadIdx.x * kCtaWarps + w] = before;
+            sHist[w * kBins + threadIdx.x] = before;
             before += c[w];
         }
     }
     __syncthreads();
+    unsigned long long ahead = w0 + lane < w1 ? load(w0 + lane) : 0ull;  // the next step's key is requested a step early
     for (int i0 = w0; i0 < w1; i0 += 32) {
         const int i = i0 + lane;
         const bool live = i < w1;
-        const unsigned long long key = live ? load(i) : 0ull;
+        const unsigned long long key = ahead;
+        ahead = i + 32 < w1 ? load(i + 32) : 0ull;
         const unsigned d = live ? ((unsigned)(key >> shift) & (kBins - 1)) : (unsigned)kBins;  // idle lanes: a group apart
         const unsigned peers = __match_any_sync(0xffffffffu, d);
         const int rank = __popc(peers & ((1u << lane) - 1u));
         int pos = 0;
-        if (live) pos = sHist[d * kCtaWarps + warp] + rank;
+        if (live) pos = sHist[warp * kBins + d] + rank;
         __syncwarp();
-        if (live && rank == 0) sHist[d * kCtaWarps + warp] += __popc(peers);  // the lowest lane of every group
+        if (live && rank == 0) sHist[warp * kBins + d] += __popc(peers);  // the lowest lane of every group
         __syncwarp();
         if (live) store(pos, key);
     }
