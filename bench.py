@@ -284,7 +284,7 @@ def config_list(args, world: int) -> list[str]:
 # the kernels of one product), with the summary under profiles/ they were read from.  A figure is attached to a
 # line only when the kernels that ran are the ones the capture covers.
 NCU_TRAFFIC = {
-    "c2": {"bytes": 281_200_000, "kernels": "SpmvLongBlockKernel + SpmvMediumShortKernel",
+    "c2": {"bytes": 280_800_000, "kernels": "SpmvLongBlockKernel + SpmvMediumShortKernel",
            "source": "profiles/spmv_binned_c2_powerlaw_f32.md"},
     "c3": {"bytes": 352_300_000, "kernels": "SpmvShortRowsKernel", "source": "profiles/spmv_binned_c3_stencil27_f16.md"},
     "c4": {"bytes": 635_600_000, "kernels": "SpmmFastKernel", "source": "profiles/spmm_fast_c4_f32_n64.md"},
