@@ -463,8 +463,9 @@ def measure_config(name: str, args, env, head: bool) -> dict:
     launch_ms_mean = max_over_ranks(e0.elapsed_time(e1) / KL)
     exchange_error = op.replication_error()
 
-    # ---- end to end: host buffers in, host result out, every step.  The package's host-operand call cuts the
-    # rows into panels so that the copies of one panel overlap the product of another.
+    # ---- end to end: host buffers in, host result out, every step, through the library's entry points for
+    # host-resident operands (include/b200sp_host.h): rows cut into panels so that the copies of one panel overlap
+    # the product of another; every copy and kernel of a step is issued by the library.
     KE = min(K, 200)
     pipe = hostio.HostOperandProduct(rp, d_ci, d_v, A.cols, dense, out, panels=args.e2e_panels)
     graph = pipe.capture(dense_h, out_h, result_h, alpha, beta) if (world == 1 and not args.no_graph) else None

@@ -25,6 +25,7 @@ SOURCES = [
     "common/context.cpp",
     "common/descr.cpp",
     "common/repeat.cpp",
+    "common/host_product.cpp",
     "spmv/spmv_host.cpp",
     "spmv/spmv_kernels.cu",
     "spmv_op/spmv_op_host.cpp",

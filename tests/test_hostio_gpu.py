@@ -77,3 +77,41 @@ def test_spmm_panels_match_one_call(pkg, handle, device):
     # every row has 64 entries: the lane-group kernel sums each in CSR order whatever the panel, same bits
     assert torch.equal(res_h.view(torch.int32), want.view(torch.int32))
     pipe.close()
+
+
+def test_c_entry_points_allocate_their_own_staging(pkg, device, oracle):
+    """include/b200sp_host.h straight through ctypes, with NULL staging buffers (the object allocates them), a
+    recorded step, a second set of scalars (a second recording) and the result written over the old y."""
+    import ctypes
+    from ctypes import POINTER, byref, c_float, c_int, c_int32, c_int64, c_void_p
+    from ops_sparse_b200 import synth, ACL_FLOAT
+    L = pkg.lib()
+    P = c_void_p
+    L.b200spHostProductCreate.argtypes = [POINTER(P), c_int64, c_int64, c_int64, POINTER(c_int32), P, P, c_int, c_int64,
+                                          c_int, c_int, P, P, c_int, c_int]
+    L.b200spHostProductRun.argtypes = [P, P, P, P, P, P, c_int]
+    L.b200spHostProductSynchronize.argtypes = [P]
+    L.b200spHostProductDestroy.argtypes = [P]
+    cfg = synth.config2(rows=1 << 14, seed=9)
+    A = cfg["A"]
+    _, d_ci, d_v = _upload(device, A)
+    rp = np.ascontiguousarray(A.row_ptr, dtype=np.int32)
+    x_h = torch.from_numpy(cfg["x"]).pin_memory()
+    y_h = torch.from_numpy(cfg["y"].copy()).pin_memory()
+    obj = P()
+    assert L.b200spHostProductCreate(byref(obj), A.rows, A.cols, A.nnz, rp.ctypes.data_as(POINTER(c_int32)),
+                                     d_ci.data_ptr(), d_v.data_ptr(), ACL_FLOAT, 0, ACL_FLOAT, ACL_FLOAT, None, None,
+                                     3, 2) == 0
+    try:
+        y_now = cfg["y"].astype(np.float32).copy()
+        for alpha, beta in ((1.5, 0.5), (1.5, 0.5), (-2.0, 0.0), (1.5, 0.5)):
+            a, b = c_float(alpha), c_float(beta)
+            assert L.b200spHostProductRun(obj, byref(a), x_h.data_ptr(), byref(b), y_h.data_ptr(), y_h.data_ptr(), 1) == 0
+            assert L.b200spHostProductSynchronize(obj) == 0
+            gold = oracle.spmv(A.row_ptr, A.col_ind, A.values, cfg["x"], y_now, alpha, beta)
+            scale = abs(alpha) * oracle.spmv_abs_rowsum(A.row_ptr, A.col_ind, A.values, cfg["x"]) + np.abs(beta * y_now)
+            helpers.assert_rowwise(y_h.numpy().astype(np.float64), gold, scale, helpers.TOL["f32"], f"alpha {alpha}")
+            y_now = y_h.numpy().copy()
+        assert L.b200spHostProductRun(obj, None, None, None, None, y_h.data_ptr(), 0) != 0  # no x: refused
+    finally:
+        assert L.b200spHostProductDestroy(obj) == 0
