@@ -545,7 +545,7 @@ def measure_config(name: str, args, env, head: bool) -> dict:
             "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "peak_source": peak_src, "kernel": kernels,
             "launch_ms_mean": launch_ms_mean, "algorithmic_bytes_per_launch": my_bytes,
             "traffic": traffic["bytes"] if traffic else None, "traffic_source": traffic["source"] if traffic else None,
-            "note": BOUND_NOTES.get(name),
+            "note": BOUND_NOTES.get(name) if world == 1 and (traffic is not None or name == "c1") else None,
         },
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE,
