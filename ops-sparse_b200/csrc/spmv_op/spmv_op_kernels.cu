@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 
 #include "b200sp_kernels.h"
+#include "../common/side_stream.h"
 
 namespace {
 
@@ -390,10 +391,22 @@ int b200sp_spmvop_launch(const void *row_offsets, int offsets_are_64, const int3
     int k = kClasses - kLongBits;  // class_start index of class kLongBits - 1
     a.first = class_start[0];
     a.count = (long long)class_start[k] - class_start[0];
+    // The rows of the ranges are disjoint, so the long-row grid goes onto the side stream and runs beside the
+    // other ranges (each of them is bound by latency, not by a throughput the others would take away).
+    b200sp::SideLanes *lanes = nullptr;
     if (a.count > 0) {
-        if (offsets_are_64) SpmvOpLongRowsKernel<true><<<(unsigned)a.count, 256, 0, st>>>(a);
-        else SpmvOpLongRowsKernel<false><<<(unsigned)a.count, 256, 0, st>>>(a);
+        cudaStream_t sL = st;
+        lanes = b200sp::GetSideLanes();
+        if (lanes != nullptr) {
+            if (cudaEventRecord(lanes->fork, st) != cudaSuccess ||
+                cudaStreamWaitEvent(lanes->stream[0], lanes->fork, 0) != cudaSuccess)
+                return (int)cudaGetLastError();
+            sL = lanes->stream[0];
+        }
+        if (offsets_are_64) SpmvOpLongRowsKernel<true><<<(unsigned)a.count, 256, 0, sL>>>(a);
+        else SpmvOpLongRowsKernel<false><<<(unsigned)a.count, 256, 0, sL>>>(a);
         b200sp_note_launches(1);
+        if (lanes != nullptr && cudaEventRecord(lanes->join[0], sL) != cudaSuccess) return (int)cudaGetLastError();
     }
     // Then one launch per run of classes that share a lane count, longest rows first.
     while (k < kClasses) {
@@ -406,6 +419,7 @@ int b200sp_spmvop_launch(const void *row_offsets, int offsets_are_64, const int3
         else LaunchRows<false>(a, G, st);
         k = k2;
     }
+    if (lanes != nullptr && cudaStreamWaitEvent(st, lanes->join[0], 0) != cudaSuccess) return (int)cudaGetLastError();
     return (int)cudaGetLastError();
 }
 
