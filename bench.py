@@ -93,9 +93,11 @@ class ClockSampler(threading.Thread):
             pass
 
     def run(self):
-        while not self._stop_evt.is_set():
+        # A query every 20 ms: a long timed region gets a series, a short one (20 steps of 90 us) gets the sample
+        # the caller takes itself while the steps run.  NVML queries go through the driver; at 500 per second on
+        # every rank they showed up in the multi-GPU step time.
+        while not self._stop_evt.wait(0.02):
             self.sample()
-            time.sleep(0.002)
 
     def stop(self) -> dict:
         self.sample()
@@ -421,16 +423,23 @@ def measure_config(name: str, args, env, head: bool) -> dict:
 
     # ---- timed region: exactly K steps, inputs resident, CUDA events on the launching stream
     sampler = ClockSampler(physical_gpu_index(env.local))
-    sampler.start()
+    if rank == 0:  # rank 0 reports its GPU's clocks; the other ranks' GPUs are left alone while they are timed
+        sampler.start()
     count = L.b200sp_kernel_launches
     count.restype = ctypes.c_ulonglong
+    if world > 1:
+        # The host-side barrier releases the ranks some hundred microseconds apart, which is a quarter of 20 steps
+        # of 60 us and would be charged to whichever rank left it first.  One more untimed step, enqueued right
+        # before the first event, lines the GPUs up on the device: its exchange waits for every rank.
+        steps(1, True)
     launches_before = count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     steps(K, True)
     e1.record()
     launches = int(count() - launches_before)  # this rank's kernels inside the timed region
-    sampler.sample()
+    if rank == 0:
+        sampler.sample()  # taken while the K steps are running on the device
     torch.cuda.synchronize()
     clocks = sampler.stop()
     barrier()
@@ -599,7 +608,8 @@ def gpu_arm(args, synth, oracle):
             "parallelism": ("single GPU" if env.world == 1 else
                             f"rows split by nnz over {env.world} GPUs; x / B held in {env.world} slices and replicated "
                             f"inside every step ({args.replicate}); 30 untimed steps before the warm-up bring the "
-                            "exchange to its steady state"),
+                            "exchange to its steady state; one untimed step after the barrier lines the ranks up "
+                            "on the device before the first event"),
             "analysis": "aclsparse*Preprocess once, outside the timed region",
             "step_issue": ("compiled loop over the C API (b200spRepeatSpMV / b200spRepeatSpMM)" if env.world == 1
                            else ("compiled loop over the C API (b200spMgRepeatSpMV / b200spMgRepeatSpMM): one exchange "
