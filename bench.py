@@ -397,8 +397,7 @@ def measure_config(name: str, args, env, head: bool) -> dict:
         elif with_exchange:
             op.steps(alpha, beta, count)  # the compiled loop again when the peer exchange is in use
         else:
-            for _ in range(count):
-                op.step(alpha, beta, broadcast=False)
+            op.products(alpha, beta, count)  # no exchange: the local product alone, same compiled loop
 
     def barrier():
         torch.cuda.synchronize()

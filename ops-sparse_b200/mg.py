@@ -240,6 +240,28 @@ class _Sharded:
     def replication_error(self) -> int:
         return self.exchange.error() if self.exchange is not None else 0
 
+    def products(self, alpha, beta, count: int) -> None:
+        """`count` local products without an exchange, against the operand as the last exchange left it, issued
+        by the library's compiled loop (include/b200sp_bench.h): what a step costs when nothing is replicated."""
+        import torch
+
+        spmm = hasattr(self, "Bs")
+        dense = (self.Bs if spmm else self.xs)[getattr(self, "_last", 0)]
+        out = self.C if spmm else self.y
+        api, L = self.api, self.api.lib()
+        ct = api._compute_type(self.A.values, out.values)
+        a_c, b_c = (ctypes.c_int32(int(alpha)), ctypes.c_int32(int(beta))) if ct == api.ACL_INT32 else \
+            (ctypes.c_float(alpha), ctypes.c_float(beta))
+        with torch.cuda.device(out.values.device):
+            if spmm:
+                rc = L.b200spRepeatSpMM(self.handle.raw, 0, 0, byref(a_c), self.A.raw, dense.raw, byref(b_c), out.raw, ct,
+                                        0, api._ptr(self.buffer), int(count))
+            else:
+                rc = L.b200spRepeatSpMV(self.handle.raw, 0, byref(a_c), self.A.raw, dense.raw, byref(b_c), out.raw, ct, 0,
+                                        api._ptr(self.buffer), int(count))
+        if rc != 0:
+            raise RuntimeError(f"compiled product loop returned status {rc}")
+
     def _compiled_steps(self, alpha, beta, count, spmm: bool) -> bool:
         """`count` steps (exchange + product) issued by the library's compiled loop (include/b200sp_bench.h)
         instead of one Python call per launch; only for the peer exchange.  Returns False when not applicable."""
