@@ -98,6 +98,48 @@ def test_csrsort(pkg, handle, device, oracle, m, n, mean_len, dups, base):
     assert L.aclsparseDestroyMatDescr(descr) == 0
 
 
+@pytest.mark.parametrize("base", [0, 1])
+@pytest.mark.parametrize("n,dups", [(200, True), (70000, False), (1 << 25, False), (2**31 - 2, False)])
+def test_csrsort_every_tier_boundary(pkg, handle, device, oracle, n, dups, base):
+    """Rows whose lengths sit on every boundary of the segmented sort (one key per lane, 2 / 4 / 8 keys per lane,
+    the CTA radix sort in shared memory, the same in global memory), with column ranges that need one to four
+    radix passes, duplicates (stability) and a permutation P that is not the identity."""
+    from ctypes import byref, c_size_t, c_void_p
+    L = pkg.lib()
+    rng = np.random.default_rng(n % 1000 + base)
+    lengths = np.array([0, 1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 300, 511, 2047, 2048, 2049,
+                        4097, 9000, 5, 0, 64, 33, 256, 2048], dtype=np.int64)
+    if not dups:
+        lengths = np.minimum(lengths, n)
+    m = lengths.size
+    rp = np.zeros(m + 1, np.int32)
+    rp[1:] = np.cumsum(lengths)
+    nnz = int(rp[-1])
+    if dups:
+        cols = [rng.integers(0, n, size=int(k)) for k in lengths]
+    else:  # distinct columns without materialising a permutation of n
+        cols = [np.unique(rng.integers(0, n, size=int(2 * k) + 8))[:int(k)] if k else np.zeros(0, np.int64) for k in lengths]
+        cols = [rng.permutation(c) for c in cols]
+        assert all(c.size == k for c, k in zip(cols, lengths))
+    ci = np.concatenate(cols).astype(np.int32) + base
+    rp = rp + base
+    p0 = rng.permutation(nnz).astype(np.int32)
+    want_ci, want_p = oracle.csrsort(rp, ci, p0, base)
+    d_rp, d_ci, d_p = torch.from_numpy(rp).to(device), torch.from_numpy(ci).to(device), torch.from_numpy(p0).to(device)
+    descr = c_void_p()
+    assert L.aclsparseCreateMatDescr(byref(descr)) == 0
+    L.aclsparseSetMatIndexBase(descr, base)
+    size = c_size_t()
+    ptr = lambda t: c_void_p(t.data_ptr())
+    assert L.aclsparseXcsrsort_bufferSizeExt(handle.raw, m, n, nnz, ptr(d_rp), ptr(d_ci), byref(size)) == 0
+    buf = torch.empty(max(size.value, 1), dtype=torch.uint8, device=device)
+    assert L.aclsparseXcsrsort(handle.raw, m, n, nnz, descr, ptr(d_rp), ptr(d_ci), ptr(d_p), ptr(buf)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(d_ci.cpu().numpy(), want_ci)
+    assert np.array_equal(d_p.cpu().numpy(), want_p)
+    assert L.aclsparseDestroyMatDescr(descr) == 0
+
+
 def test_csrsort_lets_the_blocked_long_row_kernel_in(pkg, handle, device, oracle):
     """Unsorted long rows keep aclsparseSpMV on a CTA per long row; after csrsort (values gathered through P) the
     analysis cuts them at the column blocks of x, and the product is the same within tolerance."""
@@ -200,6 +242,41 @@ def test_csr2csc(pkg, handle, device, oracle, vt, base, numeric):
         assert np.array_equal(got_v, want_val.view(np.uint8).reshape(nnz, -1))
     else:
         assert np.all(got_v == 0x5A)  # SYMBOLIC leaves cscVal alone
+
+
+def test_csr2csc_every_tier_boundary(pkg, handle, device, oracle):
+    """Columns whose lengths sit on every boundary of the segmented sort (see the csrsort test above): the matrix is
+    the transpose of one whose ROWS have those lengths."""
+    from ctypes import byref, c_size_t, c_void_p
+    from ops_sparse_b200 import synth
+    L, S = pkg.lib(), pkg
+    rng = np.random.default_rng(77)
+    lengths = np.array([0, 1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 300, 511, 2047, 2048, 2049,
+                        4097, 9000, 5, 0, 64, 33, 256, 2048], dtype=np.int64)
+    n, m = lengths.size, 12000                                  # n columns of those lengths, m rows
+    T = synth.csr_from_lengths(rng, lengths, m, synth.normal)   # n x m: its rows are the columns wanted
+    raw_t = T.values.astype(np.float32).view(np.uint32)
+    rp, ci, raw = oracle.csr2csc(n, m, T.row_ptr, T.col_ind, raw_t, 0)   # A = T^T as CSR (m x n)
+    nnz = ci.size
+    want_cp, want_ri, want_raw = oracle.csr2csc(m, n, rp, ci, raw, 0)
+    assert np.array_equal(want_cp, T.row_ptr) and np.array_equal(want_ri, T.col_ind)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    d_rp, d_ci, d_v = dev(rp), dev(ci), dev(raw.view(np.int32))
+    o_v = torch.zeros(nnz, dtype=torch.int32, device=device)
+    o_cp = torch.full((n + 1,), -3, dtype=torch.int32, device=device)
+    o_ri = torch.full((nnz,), -3, dtype=torch.int32, device=device)
+    P = lambda t: c_void_p(t.data_ptr())
+    size = c_size_t()
+    assert L.aclsparseCsr2cscEx2_bufferSize(handle.raw, m, n, nnz, None, None, None, None, None, None, S.ACL_FLOAT, 1, 0,
+                                            0, byref(size)) == 0
+    buf = torch.empty(size.value, dtype=torch.uint8, device=device)
+    for _ in range(2):  # the second run finds the workspace dirty
+        assert L.aclsparseCsr2cscEx2(handle.raw, m, n, nnz, P(d_v), P(d_rp), P(d_ci), P(o_v), P(o_cp), P(o_ri), S.ACL_FLOAT,
+                                     1, 0, 0, P(buf)) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(o_cp.cpu().numpy(), want_cp)
+        assert np.array_equal(o_ri.cpu().numpy(), want_ri)
+        assert np.array_equal(o_v.cpu().numpy().view(np.uint32), want_raw)
 
 
 def test_csr2csc_empty_matrix_and_transposed_product(pkg, handle, device, oracle):
