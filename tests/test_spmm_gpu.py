@@ -385,23 +385,24 @@ def _analysed_blocks(pkg, dA, n, row_bytes):
     return blocks.value, longs.value
 
 
-@pytest.mark.parametrize("vt,n", [("bf16", 256), ("f32", 128), ("f32", 264)])
+@pytest.mark.parametrize("vt,n", [("bf16", 256), ("f16", 256), ("f32", 128), ("f32", 264)])
 def test_long_rows_by_column_blocks(pkg, handle, device, oracle, vt, n):
     """B far larger than L2 and rows of more than 1024 entries with ascending columns: the long rows are summed
     block by block of B (SpmmLongBlockKernel).  The result must satisfy the usual tolerance, be the same bits on
     every run, and the analysis must have chosen that path; with one long row's columns out of order it must not."""
     from ops_sparse_b200 import api
     rng = np.random.default_rng(97)
-    esize = 2 if vt == "bf16" else 4
+    esize = 4 if vt == "f32" else 2
     k = (120 << 20) // (n * esize)              # B of about 120 MB
     m = 1500
     A = _block_case(rng, m, k, 40, 1025, 9000)
-    tdt = torch.bfloat16 if vt == "bf16" else torch.float32
+    tdt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[vt]
+    cdt = torch.float16 if vt == "f16" else torch.float32       # the reference's fp16 SpMM writes fp16
     Bq = torch.from_numpy(rng.standard_normal((k, n)).astype(np.float32)).to(tdt)
-    C0 = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32))
+    C0 = torch.from_numpy(rng.standard_normal((m, n)).astype(np.float32)).to(cdt)
     vq = torch.from_numpy(A.values).to(tdt)
     dB = api.DnMat.row_major(Bq.to(device))
-    tol = 2e-3 if vt == "bf16" else 1e-5
+    tol = 1e-5 if vt == "f32" else 2e-3
 
     def product(col_ind):
         dA = api.CsrMatrix(torch.from_numpy(A.row_ptr).to(device), torch.from_numpy(col_ind).to(device),
@@ -416,8 +417,8 @@ def test_long_rows_by_column_blocks(pkg, handle, device, oracle, vt, n):
             outs.append(dC.values.clone())
         assert torch.equal(outs[0], outs[1]), "two runs differ"
         bad, worst = oracle.check_spmm_f32(A.row_ptr, col_ind, vq.to(torch.float32).numpy(),
-                                           Bq.to(torch.float32).numpy(), C0.numpy(), outs[0].cpu().numpy(),
-                                           0.75, 0.0, tol)
+                                           Bq.to(torch.float32).numpy(), C0.to(torch.float32).numpy(),
+                                           outs[0].to(torch.float32).cpu().numpy(), 0.75, 0.0, tol)
         assert bad == 0, worst
         return _analysed_blocks(pkg, dA, n, n * esize)
 
