@@ -62,7 +62,7 @@ size_t b200sp_spmv_tile_plan_bytes(int64_t rows, int64_t nnz);
  *      synchronises.  b200sp_spmv_launch then runs the merge-path tile kernel.
  *  plan_info != NULL : binned plan.  B200SP_SPMV_PLAN_INFO_INTS ints are written to it: [0] kind = 1 or 2,
  *      [1] medium rows, [2] long rows, [3] lanes per short row, [4] column blocks of x and [5] columns per
- *      block (kind 2 only), [6] the length from which a row counts as long, [7] the 2048-entry segments the long rows
+ *      block (kind 2 only), [6] the length from which a row counts as long, [7] the 8192-entry segments the long rows
  *      were cut into (kind 1 runs a CTA per segment).  Rows are binned by length
  *      -- short (<= 32 entries), medium, long -- the medium and long rows are listed in `plan`, and the call
  *      synchronises `stream` once to read the counts back.  b200sp_spmv_launch then runs one kernel per

@@ -191,9 +191,9 @@ def test_buffer_size_formulas(pkg):
     assert 16 * tiles <= tile_plan <= 16 * tiles + 4096   # tile table + counters + two partial arrays, 4 B each
     # binned plan: a list entry per row that can be longer than 32 entries, one per possible long row (512+)
     # {row, start, end, -} per entry; the long list twice (as found, then ordered by length)
-    long_len, seg_len = 512, 2048
+    long_len, seg_len = 512, 8192
     cap_long = nnz // long_len + 1
-    cap_segs = nnz // seg_len + cap_long   # long rows cut into 2048-entry segments: {row, start, end, slot} each
+    cap_segs = nnz // seg_len + cap_long   # long rows cut into 8192-entry segments: {row, start, end, slot} each
     bins = 256 + 16 * (min(rows, nnz // 33) + 1) + 2 * 16 * cap_long
     segs = 16 * cap_segs + 8 * cap_long + 4 * cap_long + 4 * cap_segs  # + per-row {first, count}, counters, partial sums
     # too wide for the blocked long-row kernel (more than 64 blocks of 32768 columns): the lists only
