@@ -484,16 +484,21 @@ def measure_config(name: str, args, env, head: bool) -> dict:
         else:
             pipe.step(dense_h, out_h, result_h, alpha, beta, upload_dense=True)
 
-    for _ in range(3):
+    for _ in range(5):
         e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(KE):
-        e2e_step()
-        torch.cuda.synchronize()  # the caller needs the result before the next step
-    e1.record()
-    torch.cuda.synchronize()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / KE
+    # Two passes of KE steps, the quieter one counts: the leg is bound by host <-> device copies, and on a shared
+    # host another job's traffic on the same PCIe switch has doubled a pass now and then.
+    e2e_passes = []
+    for _ in range(2):
+        barrier()
+        e0.record()
+        for _ in range(KE):
+            e2e_step()
+            torch.cuda.synchronize()  # the caller needs the result before the next step
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_passes.append(max_over_ranks(e0.elapsed_time(e1)) / KE)
+    e2e_ms = min(e2e_passes)
     del graph
     pipe.close()
     out_bytes = (r1 - r0) * n * out_h.element_size()
@@ -557,6 +562,7 @@ def measure_config(name: str, args, env, head: bool) -> dict:
         },
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": KE,
+                "passes_ms": [round(v, 6) for v in e2e_passes],
                 "row_panels": args.e2e_panels, "cuda_graph": world == 1 and not args.no_graph},
         "compute_only": {"value": flops / (launch_ms_mean * 1e-3) / 1e9, "unit": "GFLOP/s",
                          "ms_per_step": launch_ms_mean,
